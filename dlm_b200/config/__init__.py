@@ -1,6 +1,7 @@
 from .base import ConfigError, read_config_json
 from .qwen2_moe import Qwen2MoeConfig
+from .salolorn import SalolornConfig
 from .zasazen import ZasazenConfig
 from .zesapel import ZesapelConfig
 
-__all__ = ["ConfigError", "read_config_json", "Qwen2MoeConfig", "ZasazenConfig", "ZesapelConfig"]
+__all__ = ["ConfigError", "read_config_json", "Qwen2MoeConfig", "SalolornConfig", "ZasazenConfig", "ZesapelConfig"]

@@ -56,13 +56,16 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
 
 // Causal (optionally windowed) attention of every token of the step over its request's paged keys and values.
 // A score is dot * scale - slopes[query head] * (query position - key position); slopes (f32 [nh], made at load,
-// never written by a kernel) == nullptr: no distance term.
+// never written by a kernel) == nullptr: no distance term.  chunk > 0: a query at p sees only keys from
+// floor(p / chunk) * chunk on (chunks are counted from a request's position 0).  sinks (f32 [nh]) != nullptr: the
+// softmax's denominator also holds exp(sinks[head]), unscaled, without key or value.
 // num_single: how many requests have exactly one query token.  With fast != 0 and a scratch buffer of
 // attention_scratch_floats(...) floats those go to the split-key decode kernel.
 void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
                const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
-               int page_size, int total_pages, int window, float scale, const float* slopes, int max_q_len,
-               int max_kv_len, int num_single, float* scratch, int dtype, int fast, cudaStream_t stream);
+               int page_size, int total_pages, int window, float scale, const float* slopes, int chunk,
+               const float* sinks, int max_q_len, int max_kv_len, int num_single, float* scratch, int dtype, int fast,
+               cudaStream_t stream);
 // Floats of scratch the decode kernel needs for a step of R requests whose longest holds max_kv_len tokens.
 size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 
@@ -229,16 +232,17 @@ void concat_rows(const float* a, const float* b, void* out, int T, int H, int ou
 
 // Per token: cq_out = rmsnorm(proj[off_q : +q_rank]) * qn_w (activation dtype); the cache row of slots[t]
 // ([rank | dr] wide, pages [pages, 1, page_size, rank + dr]) = [rmsnorm(proj[off_kv : +rank]) * kvn_w |
-// rotate(proj[off_kv + rank : +dr])].  Rotation on the first rot_dims entries, pair (i, i + rot_dims / 2).
+// rotate(proj[off_kv + rank : +dr])].  Rotation on the first rot_dims entries, pair (i, i + rot_dims / 2), or
+// (2i, 2i + 1) with interleaved != 0.  q_rank 0: there is no query latent and cq_out is not written.
 void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* qn_w, int off_kv, int rank,
-                 const float* kvn_w, int dr, const float* inv_freq, int rot_dims, const int32_t* positions,
+                 const float* kvn_w, int dr, const float* inv_freq, int rot_dims, int interleaved, const int32_t* positions,
                  const int32_t* slots, float eps, void* cq_out, void* cache, int page_size, int total_pages, int T,
                  int dtype, cudaStream_t stream);
 
 // q f32 [T, H * (dn + dr)] (per head [dn plain | dr to be rotated]) -> qn[H, T, dn] in `dtype` (head by head: the
-// left operand of the per-head product with W_uk) and qr[T, H, dr] f32, rotated.
-void latent_q_split(const float* q, int ldq, const int32_t* positions, const float* inv_freq, int rot_dims, void* qn,
-                    float* qr, int T, int H, int dn, int dr, int dtype, cudaStream_t stream);
+// left operand of the per-head product with W_uk) and qr[T, H, dr] f32, rotated (pairs as in latent_prep).
+void latent_q_split(const float* q, int ldq, const int32_t* positions, const float* inv_freq, int rot_dims,
+                    int interleaved, void* qn, float* qr, int T, int H, int dn, int dr, int dtype, cudaStream_t stream);
 // Attention over the cached latents.  q_lat f32 [H, T, rank]: the heads' queries through W_uk; q_rot f32 [T, H, dr];
 // sink f32 [H] or nullptr (a logit per head that joins the softmax's maximum and denominator only); cache
 // [pages, 1, page_size, rank + dr] and lat[H, T, rank] (the normalised weighted sums of latent rows) in `dtype`.
@@ -256,5 +260,42 @@ void latent_gate_out(const float* val, const float* gate, int ldg, void* out, in
 // Splits that fill the machine for a step of T tokens whose longest visible range is max_keys (1 in 32-bit, where
 // the order of every sum is fixed).
 int latent_attention_splits(int T, int H, int rank, int dr, int max_keys, int dtype, int fast);
+
+// ---- gated recurrences with a matrix state, per-head norms, sublayers with a norm on both sides (gatedmix.cu) ----
+
+// Recurrence over each request's tokens with a state S [dk, dv] per head (state f32 [slots, heads, dk, dv]):
+//   S <- diag(a) S;   u = beta (v - S^T k) (beta given) or u = v (beta == nullptr);   S <- S + k u^T;   o = S^T q.
+// q, k f32 rows of qk_heads heads of dk entries (row strides ldq, ldk; head h reads q/k head h / (heads / qk_heads));
+// v f32 rows of heads * dv; o f32 rows of heads * dv (stride ldo).  unit != 0: q and k are divided by
+// sqrt(sum x^2 + unit_eps) per head first; q is multiplied by q_scale.  beta f32 [T, heads] raw (sigmoid is applied).
+// decay_kind 0: one factor per head, a = exp(-exp(A_log[h]) softplus(dec[t, h] + dec_bias[h]));
+// decay_kind 1: one per key channel, a_i = sigmoid(dec[t, h * dk + i])^(1 / tau).
+void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* dec, int ldd,
+                const float* beta, int ldb, const float* A_log, const float* dec_bias, float* state,
+                const int32_t* cu_q, const int32_t* state_slot, float* o, int ldo, int R, int heads, int qk_heads,
+                int dk, int dv, int unit, float unit_eps, float q_scale, int decay_kind, float tau,
+                cudaStream_t stream);
+
+// qkv f32 rows [q: nh * d | k: nkv * d | v: nkv * dv] (row stride ld).  Every q and k head is divided by its root
+// mean square over d (eps inside the root) and multiplied by qn_w / kn_w (f32 [d], shared by the heads; nullptr: that
+// side is not normed), then its first rot_dims entries are rotated by position * inv_freq[pair] (pair i is entries
+// (i, i + rot_dims / 2), or (2i, 2i + 1) with interleaved != 0).  q goes to q_out[T, nh * D] and, where slots !=
+// nullptr and slots[t] >= 0, k and v to the paged caches [pages, nkv, page_size, D], every head D wide with zeros
+// beyond its own size (D >= d, dv).
+void head_norm_rope_write(const float* qkv, int ld, const int32_t* positions, const float* qn_w, const float* kn_w,
+                          float eps, const float* inv_freq, int rot_dims, int interleaved, const int32_t* slots,
+                          void* q_out, void* k_cache, void* v_cache, int T, int nh, int nkv, int d, int dv, int D,
+                          int page_size, int total_pages, int dtype, cudaStream_t stream);
+
+// o[t, h * D + i] *= factor * sigmoid(gate[t * ldg + h]) in place (o in `dtype`, gate f32 raw)
+void head_gate(void* o, const float* gate, int ldg, int T, int nh, int D, float factor, int dtype, cudaStream_t stream);
+
+// resid[t] += (y[t] / rms(y[t])) * w_post; then, with w_next != nullptr, out[t] = (resid[t] / rms(resid[t])) * w_next
+// in out_dtype: a sublayer's closing norm, the add to the residual and the next sublayer's opening norm in one pass.
+void norm_add_norm(float* resid, const float* y, const float* w_post, const float* w_next, float eps, void* out, int T,
+                   int H, int out_dtype, cudaStream_t stream);
+
+// x[t, :] += (x0 != nullptr ? x0[t, :] : 0) + vec[:]   (all f32)
+void add_vec_rows(float* x, const float* x0, const float* vec, int T, int H, cudaStream_t stream);
 
 }  // namespace dlmk

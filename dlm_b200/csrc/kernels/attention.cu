@@ -14,11 +14,14 @@ size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len) 
 
 void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
                const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
-               int page_size, int total_pages, int window, float scale, const float* slopes, int max_q_len,
-               int max_kv_len, int num_single, float* scratch, int dtype, int fast, cudaStream_t stream) {
-    const Score score(scale, slopes);
+               int page_size, int total_pages, int window, float scale, const float* slopes, int chunk,
+               const float* sinks, int max_q_len, int max_kv_len, int num_single, float* scratch, int dtype, int fast,
+               cudaStream_t stream) {
+    const Score score(scale, slopes, chunk, sinks);
     if (T <= 0 || R <= 0) return;
-    const bool decode = fast && num_single > 0 && scratch != nullptr && attention_decode_ok(hd);
+    DLM_CHECK(chunk >= 0, "attention: a chunk size is positive (0: none)");
+    const bool decode = fast && num_single > 0 && scratch != nullptr && attention_decode_ok(hd) &&
+                        (score.plain_mask() || attention_decode_takes(score, dtype, hd));
     if (decode) {
         int n_splits, chunk;
         attention_decode_plan(R, nkv, max_kv_len < 1 ? 1 : max_kv_len, &n_splits, &chunk);
@@ -35,7 +38,7 @@ void attention(const void* q, const void* k_cache, const void* v_cache, const in
             attention_prefill_tc(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd,
                                  page_size, total_pages, window, score, decode ? 1 : 0, stream)) {
             // done on the tcgen05 path
-        } else if (fast && dtype == BF16 && attention_prefill_ok(hd))
+        } else if (fast && dtype == BF16 && attention_prefill_ok(hd) && (score.plain_mask() || attention_prefill_takes(score)))
             attention_prefill(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd,
                               page_size, total_pages, window, score, decode ? 1 : 0, stream);
         else

@@ -9,11 +9,23 @@ namespace dlmk {
 
 // How a score is made from a dot product: dot * scale - slopes[query head] * (query position - key position);
 // slopes == nullptr: no distance term.  Converts from a plain scale.
+// chunk > 0: a query at p sees only keys j >= floor(p / chunk) * chunk (chunks are counted from position 0 of the
+// request).  sinks (f32 [nh], made at load) != nullptr: the softmax's denominator also holds exp(sinks[head]), a
+// logit without key or value that is not scaled.
 struct Score {
     float scale;
     const float* slopes;
-    Score(float s, const float* b = nullptr) : scale(s), slopes(b) {}
+    int chunk;
+    const float* sinks;
+    Score(float s, const float* b = nullptr, int c = 0, const float* k = nullptr)
+        : scale(s), slopes(b), chunk(c), sinks(k) {}
+    bool plain_mask() const { return chunk <= 0 && sinks == nullptr; }
 };
+
+// Which of the faster kernels take a chunked mask or a sink (the FMA kernel below takes both; steps whose kernel
+// does not are served by it).
+inline bool attention_prefill_takes(const Score&) { return false; }
+inline bool attention_decode_takes(const Score&, int /*dtype*/, int /*hd*/) { return false; }
 
 // FMA-unit kernel for any mix of query lengths.  skip_single != 0: requests with exactly one query token are
 // left to the decode kernel.

@@ -81,6 +81,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
     const int hi = pos0 + n_q - 1;                  // last key any query of the tile sees
     int lo = 0;
     if (window > 0) lo = max(0, pos0 - window + 1);
+    if (scale.chunk > 0) lo = max(lo, (pos0 / scale.chunk) * scale.chunk);   // the first query's chunk starts lowest
     const int tile_lo = (lo / BKV) * BKV;
     const int* table = block_table + (long long)r * table_width;
 
@@ -118,7 +119,8 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
             float s = 0.f;
             for (int d = 0; d < hd; ++d) s = fmaf(qv[d], kr[d], s);
             s = s * scale.scale - slope * (float)(p - j);
-            const bool visible = (j <= p) && (window <= 0 || p - j < window);
+            const bool visible = (j <= p) && (window <= 0 || p - j < window) &&
+                                 (scale.chunk <= 0 || j >= (p / scale.chunk) * scale.chunk);
             if (!visible) s = -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
             if (m_new == -INFINITY) continue;       // this query sees nothing in the tile
@@ -146,7 +148,14 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
     for (int i = 0; i < QPW; ++i) {
         const int qi = warp * QPW + i;
         if (qi >= n_q) continue;
-        const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+        float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+        if (scale.sinks != nullptr && l[i] > 0.f) {
+            // the sink joins maximum and denominator at the end: exp(m - M) (l + exp(sink - m)) with M = max(m, sink)
+            const float sk = scale.sinks[head];
+            const float M = fmaxf(m[i], sk);
+            const float a = expf(m[i] - M);
+            inv = a / (l[i] * a + expf(sk - M));
+        }
         T* orow = out + (long long)(q_begin + q0 + qi) * Q + head * hd;
 #pragma unroll
         for (int jd = 0; jd < DPL; ++jd) {

@@ -44,13 +44,13 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("attention", [](u64 q, u64 k_cache, u64 v_cache, u64 block_table, int table_width, u64 cu_q, u64 kv_len,
                           u64 out, int T, int R, int nh, int nkv, int hd, int page_size, int total_pages, int window,
-                          float scale, u64 slopes, int max_q_len, int max_kv_len, int num_single, u64 scratch, int dtype,
-                          int fast, u64 stream) {
+                          float scale, u64 slopes, int chunk, u64 sinks, int max_q_len, int max_kv_len, int num_single,
+                          u64 scratch, int dtype, int fast, u64 stream) {
         dlmk::attention(ptr<const void>(q), ptr<const void>(k_cache), ptr<const void>(v_cache),
                         ptr<const int32_t>(block_table), table_width, ptr<const int32_t>(cu_q),
                         ptr<const int32_t>(kv_len), ptr<void>(out), T, R, nh, nkv, hd, page_size, total_pages, window,
-                        scale, ptr<const float>(slopes), max_q_len, max_kv_len, num_single, ptr<float>(scratch), dtype,
-                        fast, st(stream));
+                        scale, ptr<const float>(slopes), chunk, ptr<const float>(sinks), max_q_len, max_kv_len,
+                        num_single, ptr<float>(scratch), dtype, fast, st(stream));
     });
     m.def("attention_scratch_floats", [](int R, int nh, int nkv, int hd, int max_kv_len) {
         return dlmk::attention_scratch_floats(R, nh, nkv, hd, max_kv_len);
@@ -184,17 +184,17 @@ PYBIND11_MODULE(_dlm_kernels, m) {
         dlmk::concat_rows(ptr<const float>(a), ptr<const float>(b), ptr<void>(out), T, H, out_dtype, st(stream));
     });
     m.def("latent_prep", [](u64 proj, int ld, int off_q, int q_rank, u64 qn_w, int off_kv, int rank, u64 kvn_w, int dr,
-                            u64 inv_freq, int rot_dims, u64 positions, u64 slots, float eps, u64 cq_out, u64 cache,
-                            int page_size, int total_pages, int T, int dtype, u64 stream) {
+                            u64 inv_freq, int rot_dims, int interleaved, u64 positions, u64 slots, float eps, u64 cq_out,
+                            u64 cache, int page_size, int total_pages, int T, int dtype, u64 stream) {
         dlmk::latent_prep(ptr<const float>(proj), ld, off_q, q_rank, ptr<const float>(qn_w), off_kv, rank,
-                          ptr<const float>(kvn_w), dr, ptr<const float>(inv_freq), rot_dims,
+                          ptr<const float>(kvn_w), dr, ptr<const float>(inv_freq), rot_dims, interleaved,
                           ptr<const int32_t>(positions), ptr<const int32_t>(slots), eps, ptr<void>(cq_out),
                           ptr<void>(cache), page_size, total_pages, T, dtype, st(stream));
     });
-    m.def("latent_q_split", [](u64 q, int ldq, u64 positions, u64 inv_freq, int rot_dims, u64 qn, u64 qr, int T, int H,
-                               int dn, int dr, int dtype, u64 stream) {
+    m.def("latent_q_split", [](u64 q, int ldq, u64 positions, u64 inv_freq, int rot_dims, int interleaved, u64 qn,
+                               u64 qr, int T, int H, int dn, int dr, int dtype, u64 stream) {
         dlmk::latent_q_split(ptr<const float>(q), ldq, ptr<const int32_t>(positions), ptr<const float>(inv_freq), rot_dims,
-                             ptr<void>(qn), ptr<float>(qr), T, H, dn, dr, dtype, st(stream));
+                             interleaved, ptr<void>(qn), ptr<float>(qr), T, H, dn, dr, dtype, st(stream));
     });
     m.def("latent_gate_out", [](u64 val, u64 gate, int ldg, u64 out, int T, int H, int dv, int dtype, u64 stream) {
         dlmk::latent_gate_out(ptr<const float>(val), ptr<const float>(gate), ldg, ptr<void>(out), T, H, dv, dtype,
@@ -211,6 +211,36 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                                fast, st(stream));
     });
     m.def("latent_attention_splits", &dlmk::latent_attention_splits);
+    m.def("gated_scan", [](u64 q, int ldq, u64 k, int ldk, u64 v, int ldv, u64 dec, int ldd, u64 beta, int ldb, u64 A_log,
+                           u64 dec_bias, u64 state, u64 cu_q, u64 state_slot, u64 o, int ldo, int R, int heads,
+                           int qk_heads, int dk, int dv, int unit, float unit_eps, float q_scale, int decay_kind,
+                           float tau, u64 stream) {
+        dlmk::gated_scan(ptr<const float>(q), ldq, ptr<const float>(k), ldk, ptr<const float>(v), ldv,
+                         ptr<const float>(dec), ldd, ptr<const float>(beta), ldb, ptr<const float>(A_log),
+                         ptr<const float>(dec_bias), ptr<float>(state), ptr<const int32_t>(cu_q),
+                         ptr<const int32_t>(state_slot), ptr<float>(o), ldo, R, heads, qk_heads, dk, dv, unit, unit_eps,
+                         q_scale, decay_kind, tau, st(stream));
+    });
+    m.def("head_norm_rope_write", [](u64 qkv, int ld, u64 positions, u64 qn_w, u64 kn_w, float eps, u64 inv_freq,
+                                     int rot_dims, int interleaved, u64 slots, u64 q_out, u64 k_cache, u64 v_cache, int T,
+                                     int nh, int nkv, int d, int dv, int D, int page_size, int total_pages, int dtype,
+                                     u64 stream) {
+        dlmk::head_norm_rope_write(ptr<const float>(qkv), ld, ptr<const int32_t>(positions), ptr<const float>(qn_w),
+                                   ptr<const float>(kn_w), eps, ptr<const float>(inv_freq), rot_dims, interleaved,
+                                   ptr<const int32_t>(slots), ptr<void>(q_out), ptr<void>(k_cache), ptr<void>(v_cache), T,
+                                   nh, nkv, d, dv, D, page_size, total_pages, dtype, st(stream));
+    });
+    m.def("head_gate", [](u64 o, u64 gate, int ldg, int T, int nh, int D, float factor, int dtype, u64 stream) {
+        dlmk::head_gate(ptr<void>(o), ptr<const float>(gate), ldg, T, nh, D, factor, dtype, st(stream));
+    });
+    m.def("norm_add_norm", [](u64 resid, u64 y, u64 w_post, u64 w_next, float eps, u64 out, int T, int H, int out_dtype,
+                              u64 stream) {
+        dlmk::norm_add_norm(ptr<float>(resid), ptr<const float>(y), ptr<const float>(w_post), ptr<const float>(w_next),
+                            eps, ptr<void>(out), T, H, out_dtype, st(stream));
+    });
+    m.def("add_vec_rows", [](u64 x, u64 x0, u64 vec, int T, int H, u64 stream) {
+        dlmk::add_vec_rows(ptr<float>(x), ptr<const float>(x0), ptr<const float>(vec), T, H, st(stream));
+    });
     m.def("take_error_flag", &dlmk::take_error_flag);
     m.def("reset_decode_merge_counters", [](u64 stream) { dlmk::reset_decode_merge_counters(st(stream)); });
     m.def("dep_launch_enabled", &dlmk::dep_launch_enabled);

@@ -27,7 +27,7 @@ namespace {
 template <typename T>
 __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int off_q, int q_rank,
                                    const float* __restrict__ qn_w, int off_kv, int rank, const float* __restrict__ kvn_w,
-                                   int dr, const float* __restrict__ inv_freq, int rot_dims,
+                                   int dr, const float* __restrict__ inv_freq, int rot_dims, int interleaved,
                                    const int32_t* __restrict__ positions, const int32_t* __restrict__ slots, float eps,
                                    T* cq_out, T* cache, int page_size, int total_pages, int* err) {
     dep_wait();          // nothing is read or written before the kernels before this one have ended
@@ -36,7 +36,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int o
     const int t = blockIdx.x;
     const float* row = proj + (long long)t * ld;
     // the query latent
-    {
+    if (q_rank > 0) {
         float part = 0.f;
         for (int i = threadIdx.x; i < q_rank; i += blockDim.x) part = fmaf(row[off_q + i], row[off_q + i], part);
         const float ss = block_sum(part, s_part);
@@ -62,7 +62,11 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int o
     const float pos = (float)positions[t];
     for (int i = threadIdx.x; i < dr; i += blockDim.x) {
         float v;
-        if (i < half) {
+        if (interleaved && i < 2 * half) {
+            float sn, cs;
+            sincosf(pos * inv_freq[i >> 1], &sn, &cs);
+            v = (i & 1) ? kr[i] * cs + kr[i - 1] * sn : kr[i] * cs - kr[i + 1] * sn;
+        } else if (i < half) {
             float sn, cs;
             sincosf(pos * inv_freq[i], &sn, &cs);
             v = kr[i] * cs - kr[i + half] * sn;
@@ -90,8 +94,8 @@ template <> struct Vec16<__nv_bfloat16> { static constexpr int n = 8; };
 // rotated parts, rotated, to qr[T, H, dr] in 32-bit.
 template <typename T>
 __global__ void latent_q_split_kernel(const float* __restrict__ q, int ldq, const int32_t* __restrict__ positions,
-                                      const float* __restrict__ inv_freq, int rot_dims, T* qn, float* qr, int Tn, int H,
-                                      int dn, int dr) {
+                                      const float* __restrict__ inv_freq, int rot_dims, int interleaved, T* qn,
+                                      float* qr, int Tn, int H, int dn, int dr) {
     dep_wait();          // nothing is read or written before the kernels before this one have ended
     dep_launch_next();
     const int t = blockIdx.x;
@@ -107,7 +111,11 @@ __global__ void latent_q_split_kernel(const float* __restrict__ q, int ldq, cons
         const float* r = row + dn;
         const int e = i - dn;
         float v;
-        if (e < half) {
+        if (interleaved && e < 2 * half) {
+            float sn, cs;
+            sincosf(pos * inv_freq[e >> 1], &sn, &cs);
+            v = (e & 1) ? r[e] * cs + r[e - 1] * sn : r[e] * cs - r[e + 1] * sn;
+        } else if (e < half) {
             float sn, cs;
             sincosf(pos * inv_freq[e], &sn, &cs);
             v = r[e] * cs - r[e + half] * sn;
@@ -565,7 +573,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, int n_spl
 }  // namespace
 
 void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* qn_w, int off_kv, int rank,
-                 const float* kvn_w, int dr, const float* inv_freq, int rot_dims, const int32_t* positions,
+                 const float* kvn_w, int dr, const float* inv_freq, int rot_dims, int interleaved, const int32_t* positions,
                  const int32_t* slots, float eps, void* cq_out, void* cache, int page_size, int total_pages, int T,
                  int dtype, cudaStream_t stream) {
     if (T <= 0) return;
@@ -573,11 +581,11 @@ void latent_prep(const float* proj, int ld, int off_q, int q_rank, const float* 
     int* err = error_flag_ptr();
     if (dtype == F32)
         launch_dep(latent_prep_kernel<float>, dim3(T), dim3(128), 0, stream, proj, ld, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq,
-                                                        rot_dims, positions, slots, eps, static_cast<float*>(cq_out),
+                                                        rot_dims, interleaved, positions, slots, eps, static_cast<float*>(cq_out),
                                                         static_cast<float*>(cache), page_size, total_pages, err);
     else
         launch_dep(latent_prep_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, 
-            proj, ld, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots, eps,
+            proj, ld, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, interleaved, positions, slots, eps,
             static_cast<__nv_bfloat16*>(cq_out), static_cast<__nv_bfloat16*>(cache), page_size, total_pages, err);
     check_launch("latent_prep");
 }
@@ -639,15 +647,15 @@ int latent_attention_splits(int T, int H, int rank, int dr, int max_keys, int dt
     return want < 1 ? 1 : want;
 }
 
-void latent_q_split(const float* q, int ldq, const int32_t* positions, const float* inv_freq, int rot_dims, void* qn,
-                    float* qr, int T, int H, int dn, int dr, int dtype, cudaStream_t stream) {
+void latent_q_split(const float* q, int ldq, const int32_t* positions, const float* inv_freq, int rot_dims,
+                    int interleaved, void* qn, float* qr, int T, int H, int dn, int dr, int dtype, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= dr, "latent_q_split: rotated dims must be even and <= dr");
     if (dtype == F32)
-        launch_dep(latent_q_split_kernel<float>, dim3(T), dim3(256), 0, stream, q, ldq, positions, inv_freq, rot_dims, static_cast<float*>(qn),
+        launch_dep(latent_q_split_kernel<float>, dim3(T), dim3(256), 0, stream, q, ldq, positions, inv_freq, rot_dims, interleaved, static_cast<float*>(qn),
                                                            qr, T, H, dn, dr);
     else
-        launch_dep(latent_q_split_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, q, ldq, positions, inv_freq, rot_dims,
+        launch_dep(latent_q_split_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, q, ldq, positions, inv_freq, rot_dims, interleaved,
                                                                    static_cast<__nv_bfloat16*>(qn), qr, T, H, dn, dr);
     check_launch("latent_q_split");
 }

@@ -293,30 +293,102 @@ class NativeOps:
 
     # ------------------------------------------------------- latent attention
     def latent_prep(self, proj, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots,
-                    eps, cache, out_dtype):
-        """Normalises the query latent (returned, activation dtype) and writes the token's cache row
-        ``[normalised latent | rotated key part]`` at its slot."""
+                    eps, cache, out_dtype, interleaved=False):
+        """Normalises the query latent (returned, activation dtype; None when ``q_rank`` is 0: the design has none)
+        and writes the token's cache row ``[normalised latent | rotated key part]`` at its slot.  ``interleaved``:
+        rotary pairs are entries (2i, 2i + 1) instead of (i, i + rot_dims / 2)."""
         T = proj.shape[0]
         total_pages, one, page_size, width = cache.shape
         assert one == 1 and width == rank + dr and cache.dtype == out_dtype and proj.dtype == torch.float32
-        cq = torch.empty((T, q_rank), dtype=out_dtype, device=proj.device)
+        cq = torch.empty((T, q_rank), dtype=out_dtype, device=proj.device) if q_rank else None
         self.launches += 1
         self.k.latent_prep(_p(proj), proj.stride(0), int(off_q), int(q_rank), _p(qn_w), int(off_kv), int(rank),
-                           _p(kvn_w), int(dr), _p(inv_freq), int(rot_dims), _p(positions), _p(slots), float(eps),
-                           _p(cq), _p(cache), page_size, total_pages, T, _dt(out_dtype), self._stream())
+                           _p(kvn_w), int(dr), _p(inv_freq), int(rot_dims), int(bool(interleaved)), _p(positions),
+                           _p(slots), float(eps), _p(cq), _p(cache), page_size, total_pages, T, _dt(out_dtype),
+                           self._stream())
         return cq
 
-    def latent_q_split(self, q, positions, inv_freq, rot_dims, H, dn, dr, out_dtype):
-        """Per head ``[dn plain | dr to be rotated]`` of ``q [T, H * (dn + dr)]`` (32-bit) -> the plain parts head by
-        head ``[H, T, dn]`` in ``out_dtype`` and the rotated parts ``[T, H, dr]`` in 32-bit."""
+    def latent_q_split(self, q, positions, inv_freq, rot_dims, H, dn, dr, out_dtype, interleaved=False):
+        """Per head ``[dn plain | dr to be rotated]`` of ``q [T, H * (dn + dr)]`` (32-bit, may be a column slice) ->
+        the plain parts head by head ``[H, T, dn]`` in ``out_dtype`` and the rotated parts ``[T, H, dr]`` in 32-bit."""
         T = q.shape[0]
         assert q.dtype == torch.float32 and q.shape[1] == H * (dn + dr) and q.stride(1) == 1
         qn = torch.empty((H, T, dn), dtype=out_dtype, device=q.device)
         qr = torch.empty((T, H, dr), dtype=torch.float32, device=q.device)
         self.launches += 1
-        self.k.latent_q_split(_p(q), q.stride(0), _p(positions), _p(inv_freq), int(rot_dims), _p(qn), _p(qr), T, H, dn,
-                              dr, _dt(out_dtype), self._stream())
+        self.k.latent_q_split(_p(q), q.stride(0), _p(positions), _p(inv_freq), int(rot_dims), int(bool(interleaved)),
+                              _p(qn), _p(qr), T, H, dn, dr, _dt(out_dtype), self._stream())
         return qn, qr
+
+    # ------------------------------------- gated recurrences, per-head norms, norms on both sides of a sublayer
+    def gated_scan(self, q, k, v, decay, beta, state, batch, heads, qk_heads, dk, dv, *, unit_eps=None, q_scale=1.0,
+                   A_log=None, decay_bias=None, tau=None):
+        """Recurrence with a state ``S [dk, dv]`` per head over each request's tokens: ``S <- diag(a) S``;
+        ``u = beta (v - S^T k)`` (``beta`` raw ``[T, heads]``, sigmoid applied) or ``u = v`` (``beta`` None);
+        ``S += k u^T``; ``o = S^T q``.  ``q, k [T, qk_heads * dk]``, ``v [T, heads * dv]``, all 32-bit and possibly
+        column slices.  ``unit_eps`` given: q and k become unit vectors per head first; q is multiplied by
+        ``q_scale``.  The decay is one per head, ``exp(-exp(A_log) softplus(decay + decay_bias))`` with ``decay``
+        ``[T, heads]`` (``A_log`` given), or one per key channel, ``sigmoid(decay)^(1 / tau)`` with ``decay``
+        ``[T, heads * dk]`` (``tau`` given).  ``state [slots, heads, dk, dv]`` is read and left up to date.  Returns o
+        ``[T, heads * dv]`` in 32-bit."""
+        T = v.shape[0]
+        per_head = A_log is not None
+        assert per_head != (tau is not None), "one decay per head (A_log) or one per key channel (tau)"
+        for t in (q, k, v, decay) + ((beta,) if beta is not None else ()):
+            assert t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == T
+        assert q.shape[1] == qk_heads * dk and k.shape[1] == qk_heads * dk and v.shape[1] == heads * dv
+        assert decay.shape[1] == (heads if per_head else heads * dk) and (beta is None or beta.shape[1] == heads)
+        assert state.shape[1:] == (heads, dk, dv) and state.dtype == torch.float32
+        o = torch.empty((T, heads * dv), dtype=torch.float32, device=v.device)
+        self.launches += 1
+        self.k.gated_scan(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(decay), decay.stride(0),
+                          _p(beta), 0 if beta is None else beta.stride(0), _p(A_log), _p(decay_bias), _p(state),
+                          _p(batch.cu_q), _p(batch.state_slot), _p(o), heads * dv, batch.num_requests, heads, qk_heads,
+                          dk, dv, int(unit_eps is not None), float(unit_eps or 0.0), float(q_scale),
+                          0 if per_head else 1, float(tau or 0.0), self._stream())
+        return o
+
+    def head_norm_rope_write(self, qkv, positions, qn_w, kn_w, eps, inv_freq, rot_dims, interleaved, slots, k_cache,
+                             v_cache, nh, nkv, d, dv, D, out_dtype):
+        """RMS norm of every query and key head over its ``d`` entries (weights ``[d]`` shared by the heads; None: no
+        norm), rotary positions on the first ``rot_dims`` entries, q returned ``[T, nh * D]`` and k, v written at the
+        tokens' slots, every head ``D`` wide (zeros beyond its own size)."""
+        T = qkv.shape[0]
+        assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] >= (nh + nkv) * d + nkv * dv
+        total_pages, nkv_c, page_size, D_c = k_cache.shape
+        assert (nkv_c, D_c) == (nkv, D) and k_cache.dtype == out_dtype and v_cache.shape == k_cache.shape
+        q = torch.empty((T, nh * D), dtype=out_dtype, device=qkv.device)
+        self.launches += 1
+        self.k.head_norm_rope_write(_p(qkv), qkv.stride(0), _p(positions), _p(qn_w), _p(kn_w), float(eps), _p(inv_freq),
+                                    int(rot_dims), int(bool(interleaved)), _p(slots), _p(q), _p(k_cache), _p(v_cache), T,
+                                    nh, nkv, d, dv, D, page_size, total_pages, _dt(out_dtype), self._stream())
+        return q
+
+    def head_gate(self, o, gate, nh, D, factor=1.0):
+        """``o[t, h * D + i] *= factor * sigmoid(gate[t, h])`` in place (``gate`` 32-bit, may be a column slice)."""
+        T = o.shape[0]
+        assert o.shape[1] == nh * D and o.is_contiguous() and gate.dtype == torch.float32 and gate.shape == (T, nh)
+        self.launches += 1
+        self.k.head_gate(_p(o), _p(gate), gate.stride(0), T, nh, D, float(factor), _dt(o.dtype), self._stream())
+
+    def norm_add_norm(self, resid, y, w_post, w_next, eps, out_dtype):
+        """``resid += rms_norm(y) * w_post``; then, with ``w_next``, returns ``rms_norm(resid) * w_next`` in
+        ``out_dtype`` (else None): a sublayer's closing norm, the add and the next sublayer's opening norm in one pass."""
+        T, H = resid.shape
+        assert resid.dtype == torch.float32 and resid.is_contiguous() and y.shape == (T, H) and y.is_contiguous()
+        out = torch.empty((T, H), dtype=out_dtype, device=resid.device) if w_next is not None else None
+        self.launches += 1
+        self.k.norm_add_norm(_p(resid), _p(y), _p(w_post), _p(w_next), float(eps), _p(out), T, H, _dt(out_dtype),
+                             self._stream())
+        return out
+
+    def add_vec_rows(self, x, x0, vec):
+        """``x[t] += x0[t] + vec`` in place (``x0`` None: only the vector); all 32-bit."""
+        T, H = x.shape
+        assert x.dtype == torch.float32 and x.is_contiguous() and vec.shape == (H,) and vec.is_contiguous()
+        assert x0 is None or (x0.shape == (T, H) and x0.is_contiguous() and x0.dtype == torch.float32)
+        self.launches += 1
+        self.k.add_vec_rows(_p(x), _p(x0), _p(vec), T, H, self._stream())
 
     def head_offsets(self, H, T, device):
         """``[0, T, 2T, ..., H T]``: the groups of a grouped product whose groups are heads (kept: built once)."""
@@ -476,8 +548,10 @@ class NativeOps:
         return q
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len, num_single=0, slopes=None):
-        """``slopes`` (32-bit ``[nh]`` or None): a score loses ``slopes[head] * (query position - key position)``."""
+                  max_kv_len, num_single=0, slopes=None, chunk=0, sinks=None):
+        """``slopes`` (32-bit ``[nh]`` or None): a score loses ``slopes[head] * (query position - key position)``.
+        ``chunk`` > 0: a query at p sees only keys from ``floor(p / chunk) * chunk`` on.  ``sinks`` (32-bit ``[nh]`` or
+        None): the softmax's denominator also holds ``exp(sinks[head])``."""
         T = q.shape[0]
         R, width = block_table.shape
         total_pages, _, page_size, _ = k_cache.shape
@@ -491,8 +565,9 @@ class NativeOps:
         decode_kernels = 1 if (q.dtype == torch.bfloat16 and hd in (16, 32, 48, 64, 96, 128)) else 2
         self.launches += 1 if scratch is None else (decode_kernels if num_single == R else decode_kernels + 1)
         self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
-                         nh, nkv, hd, page_size, total_pages, int(window), float(scale), _p(slopes), int(max_q_len),
-                         int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast, self._stream())
+                         nh, nkv, hd, page_size, total_pages, int(window), float(scale), _p(slopes), int(chunk), _p(sinks),
+                         int(max_q_len), int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast,
+                         self._stream())
         return out
 
     # ------------------------------------------------------------------- moe

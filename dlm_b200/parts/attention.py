@@ -90,16 +90,21 @@ class LatentAttention(Mixer):
     all).  The softmax's denominator also holds ``exp(sink_n)``, a learned logit per head without key or value.
     Head n's output is multiplied by ``sigmoid(W_g h)_n``; then ``W_o``.
 
+    ``q_rank`` None: there is no query latent and ``q = W_q h`` (tensor ``q``).  ``interleaved``: the rotation
+    pairs entries ``(2i, 2i + 1)`` instead.
+
     Only ``[c | rotated k_rot]`` is cached (one paged tensor, ``kv_rank + rot_dim`` wide).  The kernels work on
     the latent: ``q' = W_uk,n^T q_plain`` meets c directly and the weighted sum of latents goes through
     ``W_uv,n`` at the end, so neither keys nor values of a head are ever built.  Both per-head products are one
     grouped matrix product each, with the heads as groups (``latent_attend``)."""
 
-    def __init__(self, hidden_size: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int,
-                 eps: float, rope_base: float, rope_dims: int | None = None, window: int | None = None,
-                 scale: float | None = None, sink: bool = True, gate: bool = True):
+    def __init__(self, hidden_size: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
+                 q_rank: int | None, eps: float, rope_base: float, rope_dims: int | None = None,
+                 window: int | None = None, scale: float | None = None, sink: bool = True, gate: bool = True,
+                 interleaved: bool = False):
         self.hidden, self.H, self.dn, self.dr, self.dv = int(hidden_size), int(heads), int(dim), int(rot_dim), int(vdim)
-        self.rank, self.q_rank, self.eps = int(kv_rank), int(q_rank), float(eps)
+        self.rank, self.q_rank, self.eps = int(kv_rank), int(q_rank) if q_rank else 0, float(eps)
+        self.interleaved = bool(interleaved)
         self.rope_base = float(rope_base)
         self.rope_dims = int(rope_dims) if rope_dims is not None else self.dr
         if self.rope_dims % 2 or not (0 <= self.rope_dims <= self.dr):
@@ -112,9 +117,12 @@ class LatentAttention(Mixer):
 
     def param_specs(self):
         H, dn, dr, dv = self.H, self.dn, self.dr, self.dv
-        specs = [ParamSpec("dq", (self.q_rank, self.hidden)), ParamSpec("dq.norm", (self.q_rank,), init="norm"),
-                 ParamSpec("uq", (H * (dn + dr), self.q_rank)),
-                 ParamSpec("dkv", (self.rank + dr, self.hidden)), ParamSpec("dkv.norm", (self.rank,), init="norm"),
+        if self.q_rank:
+            specs = [ParamSpec("dq", (self.q_rank, self.hidden)), ParamSpec("dq.norm", (self.q_rank,), init="norm"),
+                     ParamSpec("uq", (H * (dn + dr), self.q_rank))]
+        else:
+            specs = [ParamSpec("q", (H * (dn + dr), self.hidden))]
+        specs += [ParamSpec("dkv", (self.rank + dr, self.hidden)), ParamSpec("dkv.norm", (self.rank,), init="norm"),
                  ParamSpec("uk", (H * dn, self.rank)), ParamSpec("uv", (H * dv, self.rank)),
                  ParamSpec("o", (self.hidden, H * dv))]
         if self.has_sink:
@@ -124,16 +132,18 @@ class LatentAttention(Mixer):
         return specs
 
     def load(self, tensors, rt: Runtime):
-        rows = [rt.matrix(tensors["dq"]), rt.matrix(tensors["dkv"])]
+        # rows [query latent, or the queries themselves | key/value latent and rotated key part | gate]
+        rows = [rt.matrix(tensors["dq" if self.q_rank else "q"]), rt.matrix(tensors["dkv"])]
         if self.has_gate:
             rows.append(rt.matrix(tensors["g"]))
         self.w_in = torch.cat(rows, dim=0).contiguous()
-        self.w_uq = rt.matrix(tensors["uq"])
+        self.w_uq = rt.matrix(tensors["uq"]) if self.q_rank else None
         # per head: W_uk transposed ([rank, dim]: the product's rows are latent entries) and W_uv as it is
         self.w_ukT = rt.matrix(tensors["uk"]).reshape(self.H, self.dn, self.rank).transpose(1, 2).contiguous()
         self.w_uv = rt.matrix(tensors["uv"]).reshape(self.H, self.dv, self.rank).contiguous()
         self.w_o = rt.matrix(tensors["o"])
-        self.qn, self.kvn = rt.vector(tensors["dq.norm"]), rt.vector(tensors["dkv.norm"])
+        self.qn = rt.vector(tensors["dq.norm"]) if self.q_rank else None
+        self.kvn = rt.vector(tensors["dkv.norm"])
         self.sink = rt.vector(tensors["sink"]) if self.has_sink else None
         self._freq = rope_inv_freqs(self.rope_dims, self.rope_base, self.rope_dims).to(rt.device) \
             if self.rope_dims else torch.zeros(1, device=rt.device)
@@ -146,17 +156,19 @@ class LatentAttention(Mixer):
         view = ctx.paged(call)
         cache = view.tensors["latent"]
         proj = ops.linear(h, self.w_in, None, torch.float32)
-        cq = ops.latent_prep(proj, 0, self.q_rank, self.qn, self.q_rank, self.rank, self.kvn, self.dr, self._freq,
+        q_cols = self.q_rank or self.H * (self.dn + self.dr)
+        cq = ops.latent_prep(proj, 0, self.q_rank, self.qn, q_cols, self.rank, self.kvn, self.dr, self._freq,
                              self.rope_dims, b.positions, view.group.slots if view.write else None, self.eps, cache,
-                             rt.dtype)
-        q = ops.linear(cq, self.w_uq, None, torch.float32)
-        gate = proj[:, self.q_rank + self.rank + self.dr:] if self.has_gate else None
+                             rt.dtype, interleaved=self.interleaved)
+        q = ops.linear(cq, self.w_uq, None, torch.float32) if self.q_rank else proj[:, :q_cols]
+        gate = proj[:, q_cols + self.rank + self.dr:] if self.has_gate else None
         o = latent_attend(ops, q, gate, self.w_ukT, self.w_uv, self.sink, cache, view.group.block_table, b, self._freq,
-                          self.rope_dims, self.window or 0, self.scale)
+                          self.rope_dims, self.window or 0, self.scale, interleaved=self.interleaved)
         ops.linear_add(o, self.w_o, resid)
 
 
-def latent_attend(ops, q, gate, w_ukT, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, window, scale):
+def latent_attend(ops, q, gate, w_ukT, w_uv, sink, cache, block_table, batch, inv_freq, rot_dims, window, scale,
+                  interleaved=False):
     """From projected queries to gated head outputs ``[T, H * vdim]`` over a cache of latents ``[c | k_rot]``.
     ``q [T, H * (dim + rot_dim)]`` 32-bit, ``gate [T, H]`` raw or None, ``w_ukT [H, rank, dim]``,
     ``w_uv [H, vdim, rank]``: split and rotate the queries; take the plain parts through W_uk (a grouped product,
@@ -165,7 +177,8 @@ def latent_attend(ops, q, gate, w_ukT, w_uv, sink, cache, block_table, batch, in
     dv = w_uv.shape[1]
     T = q.shape[0]
     dr = q.shape[1] // H - dn
-    qn, q_rot = ops.latent_q_split(q, batch.positions, inv_freq, rot_dims, H, dn, dr, cache.dtype)
+    qn, q_rot = ops.latent_q_split(q, batch.positions, inv_freq, rot_dims, H, dn, dr, cache.dtype,
+                                   interleaved=interleaved)
     offsets = ops.head_offsets(H, T, q.device)
     q_lat = ops.grouped_linear(qn.reshape(H * T, dn), w_ukT, offsets).reshape(H, T, rank)
     lat = ops.latent_attention(q_lat, q_rot, sink, cache, block_table, batch, H, dr, rank, window, scale)
@@ -248,6 +261,96 @@ class NormedBiasedAttention(Mixer):
         ops.linear_add(o, self.w_o, resid)
 
 
+class HeadNormedAttention(Mixer):
+    """Grouped-query softmax attention with a norm per head, a choice of masks, an optional sink and an optional gate.
+
+    ``q, k, v = W h`` (no biases) with ``heads`` query heads and ``kv_heads`` key/value heads (query head n reads
+    key/value head ``n // (heads / kv_heads)``), keys ``dim`` wide, values ``vdim`` wide.  With ``qk_norm`` every query
+    head is divided by its root mean square over ``dim`` and multiplied by ``q.norm`` (``[dim]``, the same for all
+    heads), every key head likewise with ``k.norm``; then the rotation (``position``: any registered rotary encoding;
+    its table, how many entries it turns and how it pairs them are the encoding's).  A score is ``(q . k) * scale``.
+    A query at p sees key ``j <= p`` iff ``p - j < window`` (when a window is given) and
+    ``floor(j / chunk) == floor(p / chunk)`` (when a chunk size is given; chunks are counted from position 0 of the
+    request).  With ``sink`` the softmax's denominator also holds ``exp(sink_n)``, a learned logit per head that has
+    no key and no value and is not scaled.  With ``gate`` head n's output is multiplied by ``sigmoid(W_g h)_n``.
+    The output is ``out_scale * W_o [heads side by side]``.
+
+    Keys and values are cached with one head size (the larger of ``dim`` and ``vdim``, rounded up to a size the
+    tensor-core kernels take; zeros beyond a head's own, zero columns in ``W_o``).  A chunked mask never looks back
+    further than ``chunk - 1`` positions, so its pages live in a windowed group of that length and go back to the
+    pool as the chunks pass."""
+
+    _HEAD_SIZES = (16, 32, 48, 64, 96, 128)
+
+    def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float,
+                 qk_norm: bool = True, position: PartSpec | None = None, window: int | None = None,
+                 chunk: int | None = None, sink: bool = False, gate: bool = False, out_scale: float = 1.0):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.hidden, self.H, self.G, self.d, self.dv = int(hidden_size), int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.eps, self.out_scale = float(scale), float(eps), float(out_scale)
+        self.qk_norm, self.has_sink, self.has_gate = bool(qk_norm), bool(sink), bool(gate)
+        self.window = int(window) if window else None
+        self.chunk = int(chunk) if chunk else None
+        self.position = build_part("position", position) if position is not None else None
+        need = max(self.d, self.dv)
+        self.D = next((s for s in self._HEAD_SIZES if s >= need), -(-need // 8) * 8)
+        self.w_in = self.w_o = self.qn = self.kn = self.sink = None
+
+    def param_specs(self):
+        H, G, d, dv = self.H, self.G, self.d, self.dv
+        specs = [ParamSpec("q", (H * d, self.hidden)), ParamSpec("k", (G * d, self.hidden)),
+                 ParamSpec("v", (G * dv, self.hidden)), ParamSpec("o", (self.hidden, H * dv))]
+        if self.qk_norm:
+            specs += [ParamSpec("q.norm", (d,), init="norm"), ParamSpec("k.norm", (d,), init="norm")]
+        if self.has_sink:
+            specs.append(ParamSpec("sink", (H,), init="bias"))
+        if self.has_gate:
+            specs.append(ParamSpec("g", (H, self.hidden)))
+        return specs
+
+    def load(self, tensors, rt: Runtime):
+        names = ("q", "k", "v", "g") if self.has_gate else ("q", "k", "v")
+        self.w_in = torch.cat([rt.matrix(tensors[n]) for n in names], dim=0).contiguous()
+        w_o = tensors["o"].to(device=rt.device, dtype=torch.float32)
+        if not self.has_gate and self.out_scale != 1.0:
+            w_o = w_o * self.out_scale             # with a gate the factor rides on the gate instead
+        if self.D != self.dv:       # zero columns where the stored heads are wider than the values
+            wide = torch.zeros((self.hidden, self.H, self.D), dtype=w_o.dtype, device=w_o.device)
+            wide[:, :, :self.dv] = w_o.reshape(self.hidden, self.H, self.dv)
+            w_o = wide.reshape(self.hidden, self.H * self.D)
+        self.w_o = rt.matrix(w_o)
+        if self.qk_norm:
+            self.qn, self.kn = rt.vector(tensors["q.norm"]), rt.vector(tensors["k.norm"])
+        self.sink = rt.vector(tensors["sink"]) if self.has_sink else None
+
+    def _span(self):
+        """How far back a query can see (None: to the start)."""
+        spans = [s for s in (self.window, self.chunk) if s]
+        return min(spans) if spans else None
+
+    def cache_need(self):
+        return PagedKV(self.G, self.D, self._span())
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        H, G, d, dv = self.H, self.G, self.d, self.dv
+        view = ctx.paged(call)
+        proj = ops.linear(h, self.w_in, None, torch.float32)               # [q | k | v | gate]
+        rot = self.position.rotary(rt) if self.position is not None else None
+        inv_freq, rot_dims = rot if rot is not None else (None, 0)
+        q = ops.head_norm_rope_write(proj, b.positions, self.qn, self.kn, self.eps, inv_freq, rot_dims,
+                                     bool(rot is not None and self.position.interleaved),
+                                     view.group.slots if view.write else None, view.k, view.v, H, G, d, dv, self.D,
+                                     rt.dtype)
+        o = ops.attention(q, view.k, view.v, view.group.block_table, b.cu_q, b.kv_len, self.window or 0, self.scale,
+                          H, G, self.D, b.max_q_len, b.max_kv_len, b.num_single, chunk=self.chunk or 0, sinks=self.sink)
+        if self.has_gate:
+            ops.head_gate(o, proj[:, (H + G) * d + G * dv:], H, self.D, self.out_scale)
+        ops.linear_add(o, self.w_o, resid)
+
+
 register_part("mixer", "gqa_attention", GroupedQueryAttention)
+register_part("mixer", "head_normed_attention", HeadNormedAttention)
 register_part("mixer", "normed_biased_attention", NormedBiasedAttention)
 register_part("mixer", "latent_attention", LatentAttention)

@@ -87,6 +87,52 @@ class ParallelBlock(PreNormBlock):
         self.mixer.forward(h1, resid, ctx, call)
 
 
+class SandwichBlock(ParallelBlock):
+    """A norm before and after each sublayer: ``x += norm1b(mixer(norm1(x)))``, then ``x += norm2b(ffn(norm2(x)))``.
+    ``ffn`` None: only the first sublayer.  When the norms are RMS norms the mixer's closing norm, the add and the
+    feed-forward's opening norm are one pass over the rows (``norm_add_norm``); otherwise each norm runs by itself."""
+
+    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm1b: PartSpec, norm2: PartSpec | None = None,
+                 ffn: PartSpec | None = None, norm2b: PartSpec | None = None, names: dict[str, str] | None = None):
+        self.norm1 = build_part("norm", norm1)
+        self.mixer = build_part("mixer", mixer)
+        self.norm1b = build_part("norm", norm1b)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.norm2 = build_part("norm", norm2) if ffn is not None else None
+        self.norm2b = build_part("norm", norm2b) if ffn is not None else None
+        self.names = {"norm1": "norm1.", "mixer": "mixer.", "norm1b": "norm1b.", "norm2": "norm2.", "ffn": "ffn.",
+                      "norm2b": "norm2b."}
+        if names:
+            self.names.update(names)
+
+    def children(self):
+        out = [(self.names["norm1"], self.norm1), (self.names["mixer"], self.mixer), (self.names["norm1b"], self.norm1b)]
+        if self.ffn is not None:
+            out += [(self.names["norm2"], self.norm2), (self.names["ffn"], self.ffn), (self.names["norm2b"], self.norm2b)]
+        return out
+
+    @staticmethod
+    def _close(resid, y, post, nxt, rt):
+        """``resid += post(y)``; returns ``nxt(resid)`` in the activation dtype when ``nxt`` is given."""
+        a = post.fusable_rms()
+        b = nxt.fusable_rms() if nxt is not None else None
+        if a is not None and (nxt is None or (b is not None and b[1] == a[1])):
+            return rt.ops.norm_add_norm(resid, y, a[0], b[0] if b is not None else None, a[1], rt.dtype)
+        resid += post.forward(y, rt, out_dtype=torch.float32)
+        return nxt.forward(resid, rt) if nxt is not None else None
+
+    def forward(self, resid, ctx: StepContext, call: int):
+        rt = ctx.rt
+        y = torch.zeros_like(resid)
+        self.mixer.forward(self.norm1.forward(resid, rt), y, ctx, call)
+        h = self._close(resid, y, self.norm1b, self.norm2, rt)
+        if self.ffn is None:
+            return
+        y.zero_()
+        self.ffn.forward(h, y, ctx, pre_norm=None)
+        self._close(resid, y, self.norm2b, None, rt)
+
+
 class HyperConnectionBlock(Part):
     """A pre-norm layer over S residual streams ``xs[:, s]`` instead of one.  For sublayer q (1: the mixer,
     2: the feed-forward) with learned ``in_q[S]``, ``mix_q[S, S]`` (indexed [from, to]) and ``out_q[S]``::
@@ -198,4 +244,5 @@ class HyperConnectionBlock(Part):
 
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "parallel", ParallelBlock)
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "hyper_connections", HyperConnectionBlock)

@@ -32,4 +32,26 @@ class InputInjection(Part):
         return rt.ops.linear(both, self.w, self.step[t], torch.float32)
 
 
+class AdditiveEntry(Part):
+    """Before pass t of a repeated run: ``x <- x + x0 + step[t]`` for t > 0 and ``x <- x + step[0]`` for the first pass,
+    with x0 the embedded tokens and ``step`` ``[passes, hidden]``; all of it 32-bit, in place."""
+
+    def __init__(self, hidden_size: int, passes: int, step: str = "step"):
+        self.hidden, self.passes, self.n_step = int(hidden_size), int(passes), str(step)
+        self.step = None
+
+    def param_specs(self):
+        return [ParamSpec(self.n_step, (self.passes, self.hidden), init="bias")]
+
+    def load(self, tensors, rt: Runtime):
+        self.step = rt.vector(tensors[self.n_step])
+
+    def forward(self, x: torch.Tensor, x0: torch.Tensor, t: int, rt: Runtime) -> torch.Tensor:
+        if not (0 <= t < self.passes):
+            raise ValueError(f"pass {t} of {self.passes}")
+        rt.ops.add_vec_rows(x, x0 if t > 0 else None, self.step[t])
+        return x
+
+
 register_part("entry", "input_injection", InputInjection)
+register_part("entry", "additive", AdditiveEntry)

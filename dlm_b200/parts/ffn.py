@@ -19,18 +19,23 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 class DenseSwiGLU(FeedForward):
     """``resid += down · (silu(gate·h) ⊙ up·h)`` without biases (src/forward/cpu.rs:966-971, 1198)."""
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, names: dict[str, str] | None = None):
+        """``names``: the three tensors' names, by default the ones of Qwen2-MoE checkpoints."""
         self.hidden, self.inter = int(hidden_size), int(intermediate_size)
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        if names:
+            self.names.update(names)
         self.w_gate_up = self.w_down = None
 
     def param_specs(self):
-        return [ParamSpec("gate_proj.weight", (self.inter, self.hidden)),
-                ParamSpec("up_proj.weight", (self.inter, self.hidden)),
-                ParamSpec("down_proj.weight", (self.hidden, self.inter))]
+        nm = self.names
+        return [ParamSpec(nm["gate"], (self.inter, self.hidden)), ParamSpec(nm["up"], (self.inter, self.hidden)),
+                ParamSpec(nm["down"], (self.hidden, self.inter))]
 
     def load(self, tensors, rt: Runtime):
-        self.w_gate_up = interleave_gate_up(rt.matrix(tensors["gate_proj.weight"]), rt.matrix(tensors["up_proj.weight"]))
-        self.w_down = rt.matrix(tensors["down_proj.weight"])
+        nm = self.names
+        self.w_gate_up = interleave_gate_up(rt.matrix(tensors[nm["gate"]]), rt.matrix(tensors[nm["up"]]))
+        self.w_down = rt.matrix(tensors[nm["down"]])
 
     def forward(self, h, resid, ctx: StepContext, pre_norm=None):
         ops = ctx.rt.ops

@@ -11,10 +11,11 @@ class RMSNorm(Norm):
     """``out = (x / sqrt(mean(x^2) + eps)) * weight`` with 32-bit statistics
     (src/forward/cpu.rs:934-942); the result is stored in the activation dtype."""
 
-    def __init__(self, size: int, eps: float, param: str = "weight"):
+    def __init__(self, size: int, eps: float, param: str = "weight", scale: float = 1.0):
         """``param``: the weight tensor's name relative to the part's prefix ("" when the prefix is the
-        whole name)."""
-        self.size, self.eps, self.param = int(size), float(eps), str(param)
+        whole name).  ``scale``: a factor on the output (it joins the 32-bit weight at load): a model whose logits
+        are its head's product times a constant gives that constant to its final norm."""
+        self.size, self.eps, self.param, self.scale = int(size), float(eps), str(param), float(scale)
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
@@ -22,6 +23,8 @@ class RMSNorm(Norm):
 
     def load(self, tensors, rt: Runtime):
         self.weight = rt.vector(tensors[self.param])
+        if self.scale != 1.0:
+            self.weight = (self.weight * self.scale).contiguous()
 
     def forward(self, x, rt: Runtime, rows=None, out_dtype=None):
         return rt.ops.rmsnorm(x, self.weight, self.eps, out_dtype or rt.dtype, rows)

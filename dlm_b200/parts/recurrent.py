@@ -227,14 +227,130 @@ class RetentionMixer(Mixer):
         ops.linear_add(g, self.w_o, resid)
 
 
+class GatedDeltaMixer(Mixer):
+    """Delta-rule recurrence with one decay per head.  ``q, k = W h`` (``kv_heads`` x ``dim``), ``v = W h``
+    (``heads`` x ``vdim``), no biases; head n reads q/k head ``n // (heads / kv_heads)``.  Each of q, k, v passes a
+    causal convolution over time per channel (``conv_taps`` taps, no bias, the last tap meets the current token) and
+    silu; q and k then become unit vectors per head, ``x / sqrt(sum x^2 + unit_eps)``, and q is multiplied by
+    ``dim^(-1/2)``.  With ``beta = sigmoid(W_b h)`` and ``g = exp(-exp(A_log_n) softplus(W_a h + dt_bias))`` per head::
+
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q      (S: dim x vdim, 32-bit, zero at the start)
+
+    Each head's o is divided by its root mean square over ``vdim`` and multiplied by ``norm`` (``[vdim]``, the same
+    for all heads) and by ``silu(W_g h)``; then ``W_o``.  A request's state: S of every head and the convolutions'
+    last ``conv_taps - 1`` inputs.  Everything between the two projections is 32-bit."""
+
+    def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, conv_taps: int, eps: float,
+                 unit_eps: float = 1e-6):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.hidden, self.H, self.G, self.d, self.dv = int(hidden_size), int(heads), int(kv_heads), int(dim), int(vdim)
+        self.taps, self.eps, self.unit_eps = int(conv_taps), float(eps), float(unit_eps)
+        if self.taps < 1:
+            raise ValueError("the convolution has at least one tap")
+        self.C = 2 * self.G * self.d + self.H * self.dv          # channels that pass the convolution: q, k, v
+        self.w_in = self.w_o = self.conv_w = self.A_log = self.dt_bias = self.norm_w = None
+
+    def param_specs(self):
+        H, G, d, dv, hid, taps = self.H, self.G, self.d, self.dv, self.hidden, self.taps
+        return [ParamSpec("q", (G * d, hid)), ParamSpec("q.conv", (G * d, taps)),
+                ParamSpec("k", (G * d, hid)), ParamSpec("k.conv", (G * d, taps)),
+                ParamSpec("v", (H * dv, hid)), ParamSpec("v.conv", (H * dv, taps)),
+                ParamSpec("b", (H, hid)), ParamSpec("a", (H, hid)), ParamSpec("A_log", (H,), init="bias"),
+                ParamSpec("dt_bias", (H,), init="bias"), ParamSpec("norm", (dv,), init="norm"),
+                ParamSpec("g", (H * dv, hid)), ParamSpec("o", (hid, H * dv))]
+
+    def load(self, tensors, rt: Runtime):
+        self.w_in = torch.cat([rt.matrix(tensors[n]) for n in ("q", "k", "v", "b", "a", "g")], dim=0).contiguous()
+        self.conv_w = torch.cat([rt.vector(tensors[n + ".conv"]) for n in ("q", "k", "v")], dim=0).contiguous()
+        self.A_log, self.dt_bias = rt.vector(tensors["A_log"]), rt.vector(tensors["dt_bias"])
+        self.norm_w = rt.vector(tensors["norm"]).repeat(self.H).contiguous()      # one weight for every head
+        self.w_o = rt.matrix(tensors["o"])
+
+    def state_need(self):
+        need = {"delta": RequestState((self.H, self.d, self.dv))}
+        if self.taps > 1:
+            need["conv"] = RequestState((self.taps - 1, self.C))
+        return need
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        H, C, Gd = self.H, self.C, self.G * self.d
+        proj = ops.linear(h, self.w_in, None, torch.float32)               # [q | k | v | beta | a | gate]
+        conv_state = ctx.state(call, "conv") if self.taps > 1 else torch.empty((0, 0, C), device=h.device)
+        qkv = ops.causal_conv(proj[:, :C], self.conv_w, None, conv_state, b, False, True, torch.float32)
+        o = ops.gated_scan(qkv[:, :Gd], qkv[:, Gd:2 * Gd], qkv[:, 2 * Gd:], proj[:, C + H:C + 2 * H], proj[:, C:C + H],
+                           ctx.state(call, "delta"), b, H, self.G, self.d, self.dv, unit_eps=self.unit_eps,
+                           q_scale=self.d ** -0.5, A_log=self.A_log, decay_bias=self.dt_bias)
+        g = ops.gated_rmsnorm(o, proj[:, C + 2 * H:], self.norm_w, H, self.eps, "silu_after", rt.dtype)
+        ops.linear_add(g, self.w_o, resid)
+
+
+class GatedLinearAttention(Mixer):
+    """Linear attention whose state decays per key channel by a factor made from the input.  ``q = W h * dim^(-1/2)``,
+    ``k = W h`` (heads x dim), ``v = W h`` (heads x vdim); ``alpha = sigmoid(W_a2 (W_a1 h) + a2.b)^(1 / tau)`` laid out
+    heads x dim (the width of the bottleneck is whatever ``a1`` has).  Per head::
+
+        S <- diag(alpha) S + k v^T;   o = S^T q                      (S: dim x vdim, 32-bit, zero at the start)
+
+    Each head's o is RMS-normed over ``vdim`` with ``norm`` (``[vdim]``, the same for all heads); the heads side by
+    side are multiplied by ``silu(W_g h)``; the output is ``out_scale * W_o`` of that.  The decay is worked out in
+    32-bit as ``exp(log sigmoid(z) / tau)``."""
+
+    def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, tau: float, eps: float,
+                 decay_rank: int = 16, out_scale: float = 1.0):
+        self.hidden, self.H, self.d, self.dv = int(hidden_size), int(heads), int(dim), int(vdim)
+        self.tau, self.eps, self.decay_rank, self.out_scale = float(tau), float(eps), int(decay_rank), float(out_scale)
+        if self.tau <= 0:
+            raise ValueError("tau must be positive")
+        self.w_in = self.w_a2 = self.b_a2 = self.norm_w = self.w_o = None
+        self.rank = self.decay_rank
+
+    def param_specs(self):
+        H, d, dv, hid = self.H, self.d, self.dv, self.hidden
+        return [ParamSpec("q", (H * d, hid)), ParamSpec("k", (H * d, hid)), ParamSpec("v", (H * dv, hid)),
+                ParamSpec("g", (H * dv, hid)), ParamSpec("a1", (-1, hid), arg=self.decay_rank),
+                ParamSpec("a2", (H * d, -1), arg=self.decay_rank), ParamSpec("a2.b", (H * d,), init="bias"),
+                ParamSpec("norm", (dv,), init="norm"), ParamSpec("o", (hid, H * dv))]
+
+    def load(self, tensors, rt: Runtime):
+        if tensors["a1"].shape[0] != tensors["a2"].shape[1]:
+            raise ValueError("a1 and a2 disagree about the width of the decay's bottleneck")
+        self.rank = int(tensors["a1"].shape[0])
+        self.w_in = torch.cat([rt.matrix(tensors[n]) for n in ("q", "k", "v", "g", "a1")], dim=0).contiguous()
+        self.w_a2, self.b_a2 = rt.matrix(tensors["a2"]), rt.vector(tensors["a2.b"])
+        self.norm_w = (rt.vector(tensors["norm"]) * self.out_scale).repeat(self.H).contiguous()
+        self.w_o = rt.matrix(tensors["o"])
+
+    def state_need(self):
+        return {"gla": RequestState((self.H, self.d, self.dv))}
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        H, Hd, Hv = self.H, self.H * self.d, self.H * self.dv
+        proj = ops.linear(h, self.w_in, None, torch.float32)               # [q | k | v | gate | a1 h]
+        low = proj[:, 2 * Hd + 2 * Hv:]
+        low = low.contiguous() if rt.dtype == torch.float32 else ops.activation(low, "copy", rt.dtype)
+        z = ops.linear(low, self.w_a2, self.b_a2, torch.float32)
+        o = ops.gated_scan(proj[:, :Hd], proj[:, Hd:2 * Hd], proj[:, 2 * Hd:2 * Hd + Hv], z, None,
+                           ctx.state(call, "gla"), b, H, H, self.d, self.dv, q_scale=self.d ** -0.5, tau=self.tau)
+        g = ops.gated_rmsnorm(o, proj[:, 2 * Hd + Hv:2 * Hd + 2 * Hv], self.norm_w, H, self.eps, "silu_after", rt.dtype)
+        ops.linear_add(g, self.w_o, resid)
+
+
 class ParallelMixers(Mixer):
-    """Two mixers side by side that read the same input.  Each output is RMS-normed over the model width with a
-    weight of its own (``<name>.out``); the result is ``coef`` times their sum (a half: the mean).  The children's
-    tensors lie under ``<name>.``; their caches and states are the pair's."""
+    """Two mixers side by side that read the same input.  ``combine`` ``"norm_mean"``: each output is RMS-normed over
+    the model width with a weight of its own (``<name>.out``); the result is ``coef`` times their sum (a half: the
+    mean).  ``combine`` ``"sum"``: the outputs are added as they are (a mixer that is to count with a factor takes it
+    as its own ``out_scale``); there are no tensors beside the children's.  The children's tensors lie under
+    ``<name>.``; their caches and states are the pair's."""
 
     def __init__(self, hidden_size: int, left: PartSpec, right: PartSpec, eps: float, coef: float = 0.5,
-                 names: tuple[str, str] = ("left", "right")):
+                 names: tuple[str, str] = ("left", "right"), combine: str = "norm_mean"):
         self.hidden, self.eps, self.coef = int(hidden_size), float(eps), float(coef)
+        if combine not in ("norm_mean", "sum"):
+            raise ValueError(f"unknown way to combine two mixers: {combine!r}")
+        self.combine = combine
         self.names = tuple(names)
         self.parts = (build_part("mixer", left), build_part("mixer", right))
         self.w_out = [None, None]
@@ -249,14 +365,16 @@ class ParallelMixers(Mixer):
         out = []
         for name, part in zip(self.names, self.parts):
             out += [replace(s, name=f"{name}.{s.name}") for s in part.param_specs()]
-            out.append(ParamSpec(f"{name}.out", (self.hidden,), init="norm"))
+            if self.combine == "norm_mean":
+                out.append(ParamSpec(f"{name}.out", (self.hidden,), init="norm"))
         return out
 
     def load(self, tensors, rt: Runtime):
         for i, (name, part) in enumerate(zip(self.names, self.parts)):
             mine = {f"{name}.{s.name}" for s in part.param_specs()}
             part.load({k[len(name) + 1:]: v for k, v in tensors.items() if k in mine}, rt)
-            self.w_out[i] = rt.vector(tensors[f"{name}.out"])
+            if self.combine == "norm_mean":
+                self.w_out[i] = rt.vector(tensors[f"{name}.out"])
 
     def cache_need(self):
         return next((p.cache_need() for p in self.parts if p.cache_need() is not None), None)
@@ -276,6 +394,11 @@ class ParallelMixers(Mixer):
 
     def forward(self, h, resid, ctx: StepContext, call: int):
         ops = ctx.rt.ops
+        if self.combine == "sum":
+            # both add into the same rows, one after the other (an add is a read and a write of the same place)
+            self.parts[0].forward(h, resid, ctx, call)
+            self.parts[1].forward(h, resid, ctx, call)
+            return
         outs = [torch.zeros_like(resid), torch.zeros_like(resid)]
         # neither mixer needs anything of the other: in a small step the second runs beside the first
         branch = ops.branch(h.shape[0])
@@ -286,6 +409,8 @@ class ParallelMixers(Mixer):
         ops.branch_norm_add(resid, outs[0], self.w_out[0], outs[1], self.w_out[1], self.eps, self.coef)
 
 
+register_part("mixer", "gated_delta", GatedDeltaMixer)
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "mamba1", Mamba1Mixer)
 register_part("mixer", "retention", RetentionMixer)
 register_part("mixer", "parallel_mixers", ParallelMixers)

@@ -221,25 +221,111 @@ class PlainOps:
         a, b = x[..., :half], x[..., half:rot_dims]
         return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot_dims:]], dim=-1)
 
+    @staticmethod
+    def _rotate_neighbours(x, positions, inv_freq, rot_dims):
+        if rot_dims == 0:
+            return x
+        ang = positions.to(torch.float32)[:, None] * inv_freq[None, :rot_dims // 2]
+        while ang.dim() < x.dim():
+            ang = ang.unsqueeze(1)
+        sin, cos = torch.sin(ang), torch.cos(ang)
+        a, b = x[..., 0:rot_dims:2], x[..., 1:rot_dims:2]
+        rot = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).reshape(*x.shape[:-1], rot_dims)
+        return torch.cat([rot, x[..., rot_dims:]], dim=-1)
+
     def latent_prep(self, proj, off_q, q_rank, qn_w, off_kv, rank, kvn_w, dr, inv_freq, rot_dims, positions, slots,
-                    eps, cache, out_dtype):
+                    eps, cache, out_dtype, interleaved=False):
         def rms(v, w):
             return (v * (1.0 / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))) * w
-        cq = rms(proj[:, off_q:off_q + q_rank], qn_w).to(out_dtype)
+        cq = rms(proj[:, off_q:off_q + q_rank], qn_w).to(out_dtype) if q_rank else None
         if slots is not None:
             c = rms(proj[:, off_kv:off_kv + rank], kvn_w)
-            kr = self._rotate(proj[:, off_kv + rank:off_kv + rank + dr], positions, inv_freq, rot_dims)
+            rotate = self._rotate_neighbours if interleaved else self._rotate
+            kr = rotate(proj[:, off_kv + rank:off_kv + rank + dr], positions, inv_freq, rot_dims)
             ps = cache.shape[2]
             sl = slots.long()
             ok = sl >= 0
             cache[sl[ok] // ps, 0, sl[ok] % ps, :] = torch.cat([c, kr], dim=-1)[ok].to(cache.dtype)
         return cq
 
-    def latent_q_split(self, q, positions, inv_freq, rot_dims, H, dn, dr, out_dtype):
+    def latent_q_split(self, q, positions, inv_freq, rot_dims, H, dn, dr, out_dtype, interleaved=False):
         T = q.shape[0]
         q = q.reshape(T, H, dn + dr)
         qn = q[..., :dn].transpose(0, 1).contiguous().to(out_dtype)
-        return qn, self._rotate(q[..., dn:], positions, inv_freq, rot_dims).contiguous()
+        rotate = self._rotate_neighbours if interleaved else self._rotate
+        return qn, rotate(q[..., dn:], positions, inv_freq, rot_dims).contiguous()
+
+    # ------------------------------------- gated recurrences, per-head norms, norms on both sides of a sublayer
+    def gated_scan(self, q, k, v, decay, beta, state, batch, heads, qk_heads, dk, dv, *, unit_eps=None, q_scale=1.0,
+                   A_log=None, decay_bias=None, tau=None):
+        T = v.shape[0]
+        rep = heads // qk_heads
+        q_ = q.reshape(T, qk_heads, dk)
+        k_ = k.reshape(T, qk_heads, dk)
+        if unit_eps is not None:
+            q_ = q_ / torch.sqrt((q_ * q_).sum(-1, keepdim=True) + unit_eps)
+            k_ = k_ / torch.sqrt((k_ * k_).sum(-1, keepdim=True) + unit_eps)
+        q_ = (q_ * q_scale).repeat_interleave(rep, dim=1)
+        k_ = k_.repeat_interleave(rep, dim=1)
+        v_ = v.reshape(T, heads, dv)
+        sp = torch.nn.functional.softplus
+        if A_log is not None:
+            raw = decay + (decay_bias if decay_bias is not None else 0.0)
+            a_ = torch.exp(-torch.exp(A_log) * sp(raw))[:, :, None].expand(T, heads, dk)
+        else:
+            a_ = torch.exp(-sp(-decay) / tau).reshape(T, heads, dk)
+        b_ = torch.sigmoid(beta) if beta is not None else None
+        out = torch.zeros((T, heads * dv), dtype=torch.float32, device=v.device)
+        cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
+        for r in range(batch.num_requests):
+            S = state[slots[r]]                                        # [heads, dk, dv]
+            for t in range(cu[r], cu[r + 1]):
+                S.mul_(a_[t][:, :, None])
+                u = v_[t]
+                if b_ is not None:
+                    u = b_[t][:, None] * (u - torch.einsum("hij,hi->hj", S, k_[t]))
+                S.add_(k_[t][:, :, None] * u[:, None, :])
+                out[t] = torch.einsum("hij,hi->hj", S, q_[t]).reshape(heads * dv)
+        return out
+
+    def head_norm_rope_write(self, qkv, positions, qn_w, kn_w, eps, inv_freq, rot_dims, interleaved, slots, k_cache,
+                             v_cache, nh, nkv, d, dv, D, out_dtype):
+        T = qkv.shape[0]
+        Q, K = nh * d, nkv * d
+        q, k = qkv[:, :Q].reshape(T, nh, d), qkv[:, Q:Q + K].reshape(T, nkv, d)
+        v = qkv[:, Q + K:Q + K + nkv * dv].reshape(T, nkv, dv)
+        if qn_w is not None:
+            q = (q * (1.0 / torch.sqrt((q * q).mean(-1, keepdim=True) + eps))) * qn_w
+        if kn_w is not None:
+            k = (k * (1.0 / torch.sqrt((k * k).mean(-1, keepdim=True) + eps))) * kn_w
+        if rot_dims:
+            rotate = self._rotate_neighbours if interleaved else self._rotate
+            q, k = rotate(q, positions, inv_freq, rot_dims), rotate(k, positions, inv_freq, rot_dims)
+        pad = torch.nn.functional.pad
+        if slots is not None:
+            ps = k_cache.shape[2]
+            sl = slots.long()
+            ok = sl >= 0
+            page, off = sl[ok] // ps, sl[ok] % ps
+            k_cache[page, :, off, :] = pad(k, (0, D - d))[ok].to(k_cache.dtype)
+            v_cache[page, :, off, :] = pad(v, (0, D - dv))[ok].to(v_cache.dtype)
+        return pad(q, (0, D - d)).reshape(T, nh * D).to(out_dtype)
+
+    def head_gate(self, o, gate, nh, D, factor=1.0):
+        T = o.shape[0]
+        g = factor * torch.sigmoid(gate)
+        o.copy_((_f(o).reshape(T, nh, D) * g[:, :, None]).reshape(T, nh * D).to(o.dtype))
+
+    def norm_add_norm(self, resid, y, w_post, w_next, eps, out_dtype):
+        resid += (y * (1.0 / torch.sqrt((y * y).mean(-1, keepdim=True) + eps))) * w_post
+        if w_next is None:
+            return None
+        return ((resid * (1.0 / torch.sqrt((resid * resid).mean(-1, keepdim=True) + eps))) * w_next).to(out_dtype)
+
+    def add_vec_rows(self, x, x0, vec):
+        if x0 is not None:
+            x += x0
+        x += vec
 
     def head_offsets(self, H, T, device):
         return torch.arange(0, (H + 1) * T, T, dtype=torch.int32, device=device)
@@ -362,7 +448,7 @@ class PlainOps:
         return q.reshape(T, Q).to(out_dtype)
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len, num_single=0, slopes=None):
+                  max_kv_len, num_single=0, slopes=None, chunk=0, sinks=None):
         T = q.shape[0]
         ps = k_cache.shape[2]
         out = torch.zeros((T, nh * hd), dtype=torch.float32, device=q.device)
@@ -374,6 +460,8 @@ class PlainOps:
                 continue
             first = n - q_len
             lo = max(0, first - window + 1) if window > 0 else 0
+            if chunk > 0:
+                lo = max(lo, (first // chunk) * chunk)
             pos = torch.arange(lo, n, device=q.device)
             pages = block_table[r, (pos // ps).long()].long()
             assert int(pages.min()) >= 0, "a visible key has no page"
@@ -384,12 +472,16 @@ class PlainOps:
             ok = pos[None, :] <= qpos[:, None]
             if window > 0:
                 ok &= (qpos[:, None] - pos[None, :]) < window
+            if chunk > 0:
+                ok &= torch.div(pos, chunk, rounding_mode="floor")[None, :] == torch.div(qpos, chunk, rounding_mode="floor")[:, None]
             for h in range(nh):
                 s = (qs[:, h, :] @ k[:, h // group, :].T) * scale
                 if slopes is not None:
                     s = s - slopes[h] * (qpos[:, None] - pos[None, :]).to(torch.float32)
                 s = s.masked_fill(~ok, float("-inf"))
-                p = torch.softmax(s, dim=-1)
+                if sinks is not None:
+                    s = torch.cat([s, sinks[h].expand(q_len, 1)], dim=1)
+                p = torch.softmax(s, dim=-1)[:, :pos.numel()]
                 out[cu[r]:cu[r + 1], h * hd:(h + 1) * hd] = p @ v[:, h // group, :]
         return out.to(q.dtype)
 
