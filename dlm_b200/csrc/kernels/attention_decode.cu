@@ -69,7 +69,8 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     const int h0 = kvh * group + pass * GT;                       // first query head of this block
     const int n_heads = min(GT, group - pass * GT);
     const int len = kv_len[r], p = len - 1;
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (scale.chunk > 0) lo = max(lo, (p / scale.chunk) * scale.chunk);       // a chunked mask: from the chunk's start
     // the request's own visible keys [lo, len) are cut into n_splits shares (multiples of 64 keys, at most
     // `chunk`), so that a request far shorter than the longest, or one with a window, still uses every block
     int share = (len - lo + n_splits - 1) / n_splits;
@@ -230,7 +231,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void attention_decode_merge_kernel(const float* part_o, const float* part_ml,
                                               const int32_t* __restrict__ cu_q, T* out, int nh, int hd,
-                                              int n_splits) {
+                                              int n_splits, const float* __restrict__ sinks) {
     dep_wait();
     dep_launch_next();
     const int r = blockIdx.x, h = blockIdx.y;
@@ -249,6 +250,12 @@ __global__ void attention_decode_merge_kernel(const float* part_o, const float* 
                 acc = fmaf(a, part_o[(base + s) * hd + d], acc);
                 ls = fmaf(a, part_ml[(base + s) * 2 + 1], ls);
             }
+        }
+        if (sinks != nullptr && ls > 0.f) {
+            // a sink: a logit without key or value that joins maximum and denominator
+            const float M = fmaxf(mx, sinks[h]), a = expf(mx - M);
+            acc *= a;
+            ls = fmaf(ls, a, expf(sinks[h] - M));
         }
         o[d] = from_f32<T>(ls > 0.f ? acc / ls : 0.f);
     }
@@ -346,10 +353,11 @@ void attention_decode(const void* q, const void* k_cache, const void* v_cache, c
 #undef DLM_DISPATCH
     check_launch("attention_decode");
     dim3 mgrid(R, nh);
+    const float* sinks = scale.sinks;
     if (dtype == F32)
-        launch_dep(attention_decode_merge_kernel<float>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<float>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits, sinks);
     else
-        launch_dep(attention_decode_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits, sinks);
     check_launch("attention_decode_merge");
 }
 
@@ -359,13 +367,13 @@ namespace dlmk {
 
 // The second stage alone (shared with the tensor-core decode kernel): merges the chunks' partial results.
 void attention_decode_merge(const float* part_o, const float* part_ml, const int32_t* cu_q, void* out, int R, int nh,
-                            int hd, int n_splits, int dtype, cudaStream_t stream) {
+                            int hd, int n_splits, const float* sinks, int dtype, cudaStream_t stream) {
     if (R <= 0) return;
     dim3 mgrid(R, nh);
     if (dtype == F32)
-        launch_dep(attention_decode_merge_kernel<float>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<float>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits, sinks);
     else
-        launch_dep(attention_decode_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits, sinks);
     check_launch("attention_decode_merge");
 }
 
@@ -474,7 +482,7 @@ extern "C" int dlm_b200_decode_attention_noalloc(const void* q, const void* k_ca
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     attention_decode_merge_kernel<T><<<dim3(R, nh), 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<T*>(out), nh,
-                                                                      hd, n_splits);
+                                                                      hd, n_splits, nullptr);
     e = cudaGetLastError();
     return (int)e;
 }

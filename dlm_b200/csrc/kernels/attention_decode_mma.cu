@@ -41,7 +41,7 @@ template <int HD>
 __device__ __forceinline__ void finish_block(unsigned char* smem_raw, const float (&o)[HD / 8][4], float m_a, float m_b,
                                              float l_a, float l_b, int r, int h0, int n_heads, int sp, int token,
                                              float* part_o, float* part_ml, int nh, int n_splits,
-                                             __nv_bfloat16* out, int fuse_merge) {
+                                             __nv_bfloat16* out, int fuse_merge, const float* sinks) {
     constexpr int DT = HD / 8;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -113,6 +113,12 @@ __device__ __forceinline__ void finish_block(unsigned char* smem_raw, const floa
                 ls = fmaf(a, __ldcg(part_ml + (base + s) * 2 + 1), ls);
             }
         }
+        if (sinks != nullptr && ls > 0.f) {
+            // a sink: a logit without key or value that joins maximum and denominator (natural base here)
+            const float sk = sinks[h0 + row], M = fmaxf(mx, sk), a = expf(mx - M);
+            acc *= a;
+            ls = fmaf(ls, a, expf(sk - M));
+        }
         out[(long long)token * nh * HD + (long long)(h0 + row) * HD + d] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
     }
 }
@@ -124,7 +130,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
                             int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                             float* part_o, float* part_ml, int nh, int nkv, int page_size,
                             int page_shift, int total_pages, int window, float scale_log2, const float* __restrict__ slopes,
-                            int chunk, int n_splits, int head_passes, __nv_bfloat16* out, int fuse_merge, int* err) {
+                            int mask_chunk, const float* __restrict__ sinks, int chunk, int n_splits, int head_passes,
+                            __nv_bfloat16* out, int fuse_merge, int* err) {
     constexpr int PITCH = HD + 8;
     constexpr int KS = HD / 16, DT = HD / 8, CPR = HD / 8;
     dep_wait();
@@ -142,7 +149,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
     const int h0 = kvh * group + pass * ROWS;
     const int n_heads = min(ROWS, group - pass * ROWS);
     const int len = kv_len[r], p = len - 1;
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (mask_chunk > 0) lo = max(lo, (p / mask_chunk) * mask_chunk);          // a chunked mask: from the chunk's start
     // the request's own visible keys, cut into n_splits equal shares (multiples of 16 keys): every split of a
     // request has the same work, whatever the longest request of the batch is
     const int share = (((len - lo) + n_splits - 1) / n_splits + 15) & ~15;
@@ -292,7 +300,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
     }
 
     finish_block<HD>(smem_raw, o, m_a, m_b, l_a, l_b, r, h0, n_heads, sp, token, part_o, part_ml, nh, n_splits, out,
-                     fuse_merge);
+                     fuse_merge, sinks);
 }
 
 // ------------------------------------------------------------------------------------------ with TMA
@@ -311,6 +319,8 @@ struct DecodeTmaParams {
     int nh, nkv, page_size, page_shift, total_pages, window;
     float scale_log2;
     const float* slopes;
+    int mask_chunk;
+    const float* sinks;
     int n_splits, head_passes;
     __nv_bfloat16* out; int fuse_merge;
     int* err;
@@ -343,7 +353,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int h0 = kvh * group + pass * ROWS;
     const int n_heads = min(ROWS, group - pass * ROWS);
     const int len = p.kv_len[r], pos = len - 1;
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    if (p.mask_chunk > 0) lo = max(lo, (pos / p.mask_chunk) * p.mask_chunk);  // a chunked mask: from the chunk's start
     const int share = (((len - lo) + p.n_splits - 1) / p.n_splits + 15) & ~15;
     const int j_begin = lo + sp * share, j_end = min(len, j_begin + share);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -500,7 +511,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         __syncthreads();
     }
     finish_block<HD>(smem_raw, o, m_a, m_b, l_a, l_b, r, h0, n_heads, sp, token, p.part_o, p.part_ml, p.nh, p.n_splits,
-                     p.out, p.fuse_merge);
+                     p.out, p.fuse_merge, p.sinks);
 }
 
 bool make_kv_map(CUtensorMap* map, const void* base, long long rows, int hd) {
@@ -544,8 +555,8 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
     launch_dep(kern, grid, WARPS * 32, smem, stream,
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv,
-        page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, chunk, n_splits, head_passes,
-        static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr());
+        page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk, scale.sinks, chunk, n_splits,
+        head_passes, static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr());
 }
 
 }  // namespace
@@ -580,8 +591,8 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
         splits = splits < 1 ? 1 : (splits > n_splits ? n_splits : splits);
         const dim3 tma_grid(R, nkv * head_passes, splits);
         DecodeTmaParams p{static_cast<const __nv_bfloat16*>(q), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh,
-                          nkv, page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, splits,
-                          head_passes,
+                          nkv, page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk,
+                          scale.sinks, splits, head_passes,
                           static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr()};
         // Blocks that have a multiprocessor to themselves keep six tiles in flight instead of three (8 requests
         // of 8,192 tokens: 4.72 -> 4.57 ms a step; of 1,030: 3.245 -> 3.235).
@@ -592,7 +603,7 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
                                             : launch_tma<128, 3>(tma_grid, stream, k_cache, v_cache, p));
         if (done) {
             check_launch("attention_decode_tma");
-            if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, splits, BF16, stream);
+            if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, splits, scale.sinks, BF16, stream);
             return;
         }
     }
@@ -609,7 +620,7 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
     }
 #undef DLM_DECODE
     check_launch("attention_decode_mma");
-    if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, n_splits, BF16, stream);
+    if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, n_splits, scale.sinks, BF16, stream);
 }
 
 }  // namespace dlmk

@@ -22,10 +22,10 @@ struct Score {
     bool plain_mask() const { return chunk <= 0 && sinks == nullptr; }
 };
 
-// Which of the faster kernels take a chunked mask or a sink (the FMA kernel below takes both; steps whose kernel
-// does not are served by it).
-inline bool attention_prefill_takes(const Score&) { return false; }
-inline bool attention_decode_takes(const Score&, int /*dtype*/, int /*hd*/) { return false; }
+// Which of the faster kernels take a chunked mask or a sink: the warp-level prefill kernel and every decode kernel
+// do; the tcgen05 prefill kernel does not (its steps go to the warp-level kernel then).
+inline bool attention_prefill_takes(const Score&) { return true; }
+inline bool attention_decode_takes(const Score&, int /*dtype*/, int /*hd*/) { return true; }
 
 // FMA-unit kernel for any mix of query lengths.  skip_single != 0: requests with exactly one query token are
 // left to the decode kernel.
@@ -62,7 +62,7 @@ void attention_decode(const void* q, const void* k_cache, const void* v_cache, c
                       int chunk, int dtype, cudaStream_t stream);
 
 void attention_decode_merge(const float* part_o, const float* part_ml, const int32_t* cu_q, void* out, int R, int nh,
-                            int hd, int n_splits, int dtype, cudaStream_t stream);
+                            int hd, int n_splits, const float* sinks, int dtype, cudaStream_t stream);
 // The same on the tensor-core path (bfloat16, head sizes of attention_prefill_ok); same scratch, same plan.
 void attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                           int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch,

@@ -34,8 +34,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
                          int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int R, int nh, int nkv, int page_size, int total_pages,
-                         int page_shift, int window, float scale_log2, const float* __restrict__ slopes, int skip_single, int n_sm,
-                         int* err) {
+                         int page_shift, int window, float scale_log2, const float* __restrict__ slopes, int mask_chunk,
+                         const float* __restrict__ sinks, int skip_single, int n_sm, int* err) {
     constexpr int PITCH = HD + 8;              // elements per shared-memory row (16 bytes of padding)
     constexpr int KS = HD / 16;                // k16 steps over the head dimension
     constexpr int DT = HD / 8;                 // n8 tiles of the output
@@ -92,7 +92,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     const int hi = pos0 + n_q - 1;
-    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    if (mask_chunk > 0) lo = max(lo, (pos0 / mask_chunk) * mask_chunk);     // the first query's chunk starts lowest
     const int t_begin = (lo / BKV) * BKV;
     const int n_tiles = (hi - t_begin) / BKV + 1;
     // a tile lies within one page when pages are a power of two of at least a tile (tiles are aligned)
@@ -140,6 +141,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int pa = pos0 + row_a, pb = pos0 + row_b;
     const int w_lo = pos0 + warp * 16, w_hi = w_lo + 15;         // positions of the warp's rows
     const bool warp_live = warp * 16 < n_q;                      // a warp of padding rows computes nothing
+    // chunked mask: where each row's chunk starts, and the lowest and highest start among the warp's rows
+    const int c_a = mask_chunk > 0 ? (pa / mask_chunk) * mask_chunk : 0, c_b = mask_chunk > 0 ? (pb / mask_chunk) * mask_chunk : 0;
+    const int wc_lo = mask_chunk > 0 ? (w_lo / mask_chunk) * mask_chunk : 0, wc_hi = mask_chunk > 0 ? (w_hi / mask_chunk) * mask_chunk : 0;
     const __nv_bfloat16* q_frag = Qs + (warp * 16 + lm_row) * PITCH + lm_col;
 
     float o[DT][4];
@@ -162,7 +166,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         const __nv_bfloat16* kt = Ks + (size_t)stage * BKV * PITCH;
         const __nv_bfloat16* vt = Vs + (size_t)stage * BKV * PITCH;
         // does any row of this warp see any key of the tile?
-        const bool seen = warp_live && j0 <= w_hi && (window <= 0 || j0 + BKV - 1 > w_lo - window);
+        const bool seen = warp_live && j0 <= w_hi && (window <= 0 || j0 + BKV - 1 > w_lo - window) && j0 + BKV - 1 >= wc_lo;
         if (seen) {
             // S = Q K^T for 16 rows x 64 keys
             float s[BKV / 8][4];
@@ -184,7 +188,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             }
             // scale (to base 2), mask where needed, running maximum
             float mx_a = m_a, mx_b = m_b;
-            const bool all_visible = j0 + BKV - 1 <= w_lo && (window <= 0 || w_hi - j0 < window);
+            const bool all_visible = j0 + BKV - 1 <= w_lo && (window <= 0 || w_hi - j0 < window) && j0 >= wc_hi;
             // the distance term slope * (key - p) of an entry: a part per row and tile, a part per column of the tile
             const float far_a = slope2 * (float)(j0 + 2 * t - pa), far_b = slope2 * (float)(j0 + 2 * t - pb);
             if (all_visible && slope2 == 0.f) {
@@ -214,7 +218,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     for (int c = 0; c < 4; ++c) {
                         const int key = j0 + j * 8 + 2 * t + (c & 1);
                         const int p = (c < 2) ? pa : pb;
-                        const bool vis = key <= p && (window <= 0 || p - key < window);
+                        const bool vis = key <= p && (window <= 0 || p - key < window) && key >= ((c < 2) ? c_a : c_b);
                         const float v = vis ? fmaf(s[j][c], scale_log2, fmaf(slope2, (float)(j * 8 + (c & 1)), c < 2 ? far_a : far_b))
                                             : -INFINITY;
                         s[j][c] = v;
@@ -270,7 +274,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         __syncthreads();
     }
 
-    const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+    float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+    if (sinks != nullptr) {
+        // the sink joins maximum and denominator at the end (base-2 units, as the running maxima are)
+        const float sk = sinks[head] * 1.4426950408889634f;
+        if (l_a > 0.f) {
+            const float M = fmaxf(m_a, sk), a = ex2(m_a - M);
+            inv_a = a / (l_a * a + ex2(sk - M));
+        }
+        if (l_b > 0.f) {
+            const float M = fmaxf(m_b, sk), a = ex2(m_b - M);
+            inv_b = a / (l_b * a + ex2(sk - M));
+        }
+    }
 #pragma unroll
     for (int i = 0; i < DT; ++i) {
         const int d = i * 8 + 2 * t;
@@ -296,7 +312,8 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
         static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, shift, window,
-        scale.scale * 1.4426950408889634f, scale.slopes, skip_single, sm_count(), error_flag_ptr());
+        scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk, scale.sinks, skip_single, sm_count(),
+        error_flag_ptr());
 }
 
 }  // namespace

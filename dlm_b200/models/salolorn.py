@@ -67,7 +67,7 @@ def build_spec(cfg: SalolornConfig) -> ModelSpec:
         entry = PartSpec("additive", {"hidden_size": cfg.width, "passes": cfg.loop["times"], "step": "step"})
     final = PartSpec("rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps, "param": "", "scale": cfg.logit_scale})
     return ModelSpec(hidden_size=cfg.width, vocab_size=cfg.vocab, layers=layers, layer_prefixes=prefixes,
-                     final_norm=final, final_norm_prefix="final.norm", embed_name="embed", lm_head_name="head",
+                     final_norm=final, final_norm_prefix="final.norm", embed_name="embed", lm_head_name=None,
                      tie_word_embeddings=True, order=layer_order(len(cfg.layers), cfg.loop),
                      pass_entry=entry, pass_entry_prefix="loop.")
 

@@ -32,7 +32,7 @@ class ModelSpec:
     final_norm: PartSpec
     final_norm_prefix: str = "model.norm."
     embed_name: str = "model.embed_tokens.weight"
-    lm_head_name: str = "lm_head.weight"
+    lm_head_name: str | None = "lm_head.weight"   # None: the design has no head tensor (the embedding is the head)
     tie_word_embeddings: bool = False    # True: the embedding is the head; False: tied iff the head is absent
     order: list[LayerCall] | None = None # None: every layer once, in index order
     embed_position: PartSpec | None = None   # a position encoding that acts on the embedded tokens
@@ -101,7 +101,8 @@ class DecoderModel:
                 out[prefix + p.name] = replace(p, name=prefix + p.name)
         for p in self.final_norm.param_specs():
             out[s.final_norm_prefix + p.name] = replace(p, name=s.final_norm_prefix + p.name)
-        out[s.lm_head_name] = ParamSpec(s.lm_head_name, (s.vocab_size, s.hidden_size), optional=True)
+        if s.lm_head_name is not None:
+            out[s.lm_head_name] = ParamSpec(s.lm_head_name, (s.vocab_size, s.hidden_size), optional=True)
         return out
 
     def check(self, available: dict[str, tuple[torch.dtype, tuple[int, ...]]]) -> None:
@@ -127,7 +128,7 @@ class DecoderModel:
         s, rt = self.spec, self.rt
         names = set(names)
         self.embed = rt.matrix(get(s.embed_name))
-        if s.tie_word_embeddings or s.lm_head_name not in names:
+        if s.tie_word_embeddings or s.lm_head_name is None or s.lm_head_name not in names:
             self.lm_head = self.embed                  # an alias, not a copy
         else:
             self.lm_head = rt.matrix(get(s.lm_head_name))
