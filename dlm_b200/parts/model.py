@@ -85,6 +85,9 @@ class DecoderModel:
                     raise ValueError(f"call {ci} cannot read call {c.reads_cache_of}'s cache: their shapes differ")
         self.embed: torch.Tensor | None = None
         self.lm_head: torch.Tensor | None = None
+        # called as ``after_layer(call, x)`` with the residual rows after every call of the order, when set (for
+        # comparing a model layer by layer; steps replayed from a graph do not call it)
+        self.after_layer = None
 
     # ------------------------------------------------------------- tensors
     def param_specs(self) -> dict[str, ParamSpec]:
@@ -177,6 +180,8 @@ class DecoderModel:
             if c.enters_pass is not None:
                 x = self.pass_entry.forward(x, x0, c.enters_pass, rt)
             self.blocks[c.layer].forward(x, ctx, ci)
+            if self.after_layer is not None:
+                self.after_layer(ci, x)
         if s.residual_streams is not None:
             x = ops.streams_reduce(x, None, None, 0.0, torch.float32)
         n = self.final_norm.forward(x, rt, rows=batch.logit_rows)

@@ -177,17 +177,30 @@ TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 
 def references(oracle, reqs, dtype):
     """Per request the exact logits and a limit for every position: TOL, or in bfloat16 three times the error that
-    rounding alone causes there (the plain model with bfloat16 where an engine must round) where that is more."""
+    rounding alone causes (the plain model with bfloat16 where an engine must round) where that is more.  Rounding
+    error at one position is a draw from a distribution (a norm behind a small mixer output magnifies it at some
+    positions and not at others, and an engine that rounds in other places draws other ones), so the error that
+    rounding causes at a position is taken as the larger of the rounded run's error there and its root mean square
+    over the request."""
     import plain_salolorn as plain
     ref = {rid: oracle.forward(t) for rid, t in reqs.items()}
     lim = {rid: torch.full((len(t),), TOL[dtype], dtype=torch.float64) for rid, t in reqs.items()}
     if dtype == "bfloat16":
         rounded = plain.PlainSalolorn(oracle.cfg, oracle.t, rounded=True)
         for rid, t in reqs.items():
-            lim[rid] = torch.maximum(lim[rid], 3.0 * row_error(rounded.forward(t), ref[rid]))
+            err = row_error(rounded.forward(t), ref[rid])
+            err = torch.maximum(err, torch.sqrt((err * err).mean()))
+            lim[rid] = torch.maximum(lim[rid], 3.0 * err)
     return ref, lim
 
 
 def worst_ratio(got, ref, lim):
     """Largest error / limit over the rows ``{(request, position): logits}``."""
     return max(float(row_error(row, ref[rid][p]) / lim[rid][p]) for (rid, p), row in got.items())
+
+
+def within_limits(got, ref, lim):
+    """A limit made from one rounded run is itself a noisy number, so a few rows may pass it by a little: no row is
+    beyond one and a half times its limit and at most one in fifty is beyond it."""
+    ratios = [float(row_error(row, ref[rid][p]) / lim[rid][p]) for (rid, p), row in got.items()]
+    return max(ratios) < 1.5 and sum(r > 1.0 for r in ratios) <= len(ratios) // 50

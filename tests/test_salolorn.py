@@ -272,3 +272,128 @@ def test_plain_model_passes_add_the_embedding_and_a_vector():
     assert torch.equal(x, after[3])
     y = plain.rms_norm(after[-1], tensors["final.norm"].to(F64), cfg["norm"]["eps"])
     assert torch.allclose(logits, 0.5 * (y @ tensors["embed"].to(F64).T))
+
+
+# ----------------------------------------------------------------- engine host side on the CPU
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_every_cutting_matches_the_plain_model(name, folders):
+    folder, oracle = folders[name]
+    V = CONFIGS[name]["vocab"]
+    reqs = {f"r{i}": tokens(i, n, V) for i, n in enumerate([1, 17, 41, 80])}
+    ref = {rid: oracle.forward(t) for rid, t in reqs.items()}
+    eng = cpu_engine(folder)
+    mixed, _ = cuttings.mixed(reqs, max_live=3, seed=1)
+    worst = 0.0
+    for steps in (cuttings.whole(reqs), cuttings.tail_decode(reqs, 20), cuttings.portions(reqs), mixed):
+        got = cuttings.run_trace(eng, steps)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        for (rid, p), row in got.items():
+            worst = max(worst, float(row_error(row, ref[rid][p])))
+    print(f"{name}: worst relative error {worst:.2e}")
+    assert worst < TOL["float32"]
+    assert all(p.used_pages == 0 for p in eng.cache.stats())
+
+
+def test_residual_after_every_layer_run(folders):
+    """The residual stream after each layer run of the engine against the plain model's (a repeated layer counts
+    each time)."""
+    folder, oracle = folders["A"]
+    toks = tokens(3, 23, CONFIGS["A"]["vocab"])
+    _, after = oracle.forward(toks, trace=True)
+    eng = cpu_engine(folder)
+    seen = []
+    eng.model.after_layer = lambda call, x: seen.append(x.detach().to(torch.float64).clone())
+    slot = eng.cache.open()
+    eng.step([(slot, toks, [])])
+    eng.cache.close(slot)
+    assert len(seen) == after.shape[0]
+    for i, x in enumerate(seen):
+        err = float((x - after[i]).abs().max() / after[i].abs().max())
+        assert err < 2e-5, (i, err)
+
+
+def test_slots_and_pages_are_used_again_with_fresh_state(folders):
+    """Six requests through three slots and a pool that holds only what is live: a request that takes a used slot
+    starts from zero state (both recurrences and the convolution's carried inputs) in every pass."""
+    folder, oracle = folders["A"]
+    V = CONFIGS["A"]["vocab"]
+    reqs = {f"q{i}": tokens(20 + i, n, V) for i, n in enumerate([70, 33, 129, 16, 90, 7])}
+    steps, _ = cuttings.mixed(reqs, max_live=3, seed=2)
+    peak = cuttings.peak_tokens(steps)
+    eng = cpu_engine(folder, num_pages=peak // 16, max_requests=3)
+    got = cuttings.run_trace(eng, steps)
+    worst = max(float(row_error(row, oracle.forward(reqs[rid][:p + 1])[-1])) for (rid, p), row in got.items()
+                if p in (0, 1, 2, len(reqs[rid]) - 1))
+    assert worst < TOL["float32"]
+    assert all(s.used_pages == 0 for s in eng.cache.stats())
+
+
+def test_greedy_generation_through_the_scheduler(folders):
+    """Engine.generate (scheduler, portions under a token budget, sampling, commit) against greedy decoding with the
+    plain model; batched prompts give what each gives alone."""
+    folder, oracle = folders["B"]
+    V = CONFIGS["B"]["vocab"]
+    prompts = [tokens(40, 5, V), tokens(41, 37, V), tokens(42, 1, V)]
+    eng = cpu_engine(folder, max_step_tokens=16)
+    outs = eng.generate(prompts, max_new_tokens=8)
+    for p, out in zip(prompts, outs):
+        seq = list(p)
+        for tok in out:
+            row = oracle.forward(seq)[-1]
+            top2 = torch.topk(row, 2).values
+            if float(top2[0] - top2[1]) > 1e-3:
+                assert int(torch.argmax(row)) == tok
+            seq.append(tok)
+    alone = [cpu_engine(folder).generate(p, max_new_tokens=8) for p in prompts]
+    assert alone == outs
+
+
+def test_replay_program_on_the_stand_in(folders, tmp_path, monkeypatch):
+    from dlm_b200.engine import replay, Engine
+    folder, oracle = folders["A"]
+    V = CONFIGS["A"]["vocab"]
+    reqs = {"a": tokens(50, 45, V), "b": tokens(51, 9, V)}
+    steps, _ = cuttings.mixed(reqs, max_live=2, seed=3)
+    real = Engine.from_pretrained
+    monkeypatch.setattr(Engine, "from_pretrained", classmethod(
+        lambda cls, path, **kw: real(path, **dict(kw, device="cpu", ops=PlainOps()))))
+    monkeypatch.setattr(sys, "stdin", io.StringIO("\n".join(json.dumps(s) for s in steps) + "\n"))
+    out_dir = str(tmp_path / "out")
+    assert replay.main(["--model", folder, "--dtype", "float32", "--out", out_dir, "--max-tokens", "128",
+                        "--page-size", "16", "--device", "cpu"]) == 0
+    fed = {r: 0 for r in reqs}
+    for st in steps:
+        rows = np.fromfile(os.path.join(out_dir, f"{st['step']}.f32"), dtype="<f4").reshape(-1, V)
+        k = 0
+        for e in st["entries"]:
+            ref = oracle.forward(reqs[e["id"]][:fed[e["id"]] + len(e["tokens"])])
+            for w in e["want"]:
+                assert float(row_error(torch.from_numpy(rows[k].copy()), ref[fed[e["id"]] + w])) < TOL["float32"]
+                k += 1
+            fed[e["id"]] += len(e["tokens"])
+
+
+_ALONE = {
+    "delta": delta(3, 1, 10, 6, 3),
+    "delta_one_tap": delta(2, 2, 8, 12, 1),
+    "latent": latent(2, 8, 4, 12, 16, 0.3, 100.0),
+    "pair": parallel(left(4, 2, 8, 12, 0.3, 9, 100.0, 4), right(2, 6, 10, 3.0), 0.6, 1.7),
+}
+
+
+@pytest.mark.parametrize("kinds", [("delta", "delta_one_tap"), ("latent", "latent"), ("pair",), ("pair", "delta")])
+@pytest.mark.parametrize("loop", [None, {"start": 0, "stop": 1, "times": 3}])
+def test_models_of_one_kind_of_mixer(kinds, loop, tmp_path):
+    """A model without any paged cache (recurrent layers only: tokens are still counted against the pool), one without
+    any recurrent state, and a single layer; with and without a repeated run; with and without feed-forward."""
+    cfg = one_layer(dict(_ALONE[kinds[0]], mlp=dense(24)), width=32, vocab=41, loop=loop)
+    cfg["layers"] += [dict(_ALONE[k], mlp=None) for k in kinds[1:]]
+    folder = str(tmp_path / "m")
+    oracle = plain.PlainSalolorn(cfg, write_model(cfg, folder, seed=5))
+    reqs = {"a": tokens(1, 40, 41), "b": tokens(2, 7, 41)}
+    ref = {rid: oracle.forward(t) for rid, t in reqs.items()}
+    eng = cpu_engine(folder)
+    mixed, _ = cuttings.mixed(reqs, max_live=2, seed=6)
+    for steps in (cuttings.whole(reqs), cuttings.portions(reqs, sizes=(2, 5)), mixed):
+        got = cuttings.run_trace(eng, steps)
+        assert max(float(row_error(row, ref[rid][p])) for (rid, p), row in got.items()) < TOL["float32"]
