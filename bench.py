@@ -11,6 +11,7 @@ continuous-batching workload on the windowed variant of the model (`serving`).
     python bench.py --workload kernels      # the weight-streaming product alone, by shape and row length
     python bench.py --workload zesapel      # the Zesapel design beside Qwen2-MoE at equal sizes, and its kernels alone
     python bench.py --workload zasazen      # the Zasazen design beside Qwen2-MoE at equal sizes, and its kernels alone
+    python bench.py --workload salolorn     # the Salolorn design beside a dense Qwen2 at equal sizes, and its kernels alone
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -887,6 +888,231 @@ def run_zasazen(args, pk) -> dict:
     return out
 
 
+def salolorn_config(width, vocab=32768, chunk=2048):
+    """Layer sizes that resemble a real model's: delta-rule heads of 128 x 128 with two value heads a query/key head
+    behind convolutions of four taps, a 512-wide latent with 128 + 64-wide query heads, 64-wide attention heads with
+    four query heads a key/value head inside chunks of `chunk` positions, linear-attention heads of 64 x 128 whose
+    decay comes through a bottleneck of 16, a gated feed-forward three times the width; the last three layers run
+    twice (7 layer runs)."""
+    dense = {"kind": "dense", "ff": 3 * width}
+    delta = {"type": "delta", "mlp": dense,
+             "mixer": {"heads": width // 128, "kv_heads": width // 256, "dim": 128, "vdim": 128, "conv": 4}}
+    lat = {"type": "latent_attention", "mlp": dense,
+           "mixer": {"heads": width // 128, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                     "rot": {"base": 10000.0, "dims": 64}}}
+    pair = {"type": "parallel", "mlp": dense, "mixer": {
+        "left": {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125,
+                 "mask": {"size": chunk}, "rot": {"base": 1e6, "dims": 64}},
+        "right": {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0}, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Salolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "max_positions": 8192, "loop": {"start": 1, "stop": 4, "times": 2}, "layers": [delta, dict(delta), lat, pair]}
+
+
+def qwen_config_like_salolorn(z):
+    """A dense Qwen2 (the Qwen2-MoE class with no experts) with the same width, vocabulary and feed-forward and as
+    many layers as the design has layer runs; attention heads of the same number and size as the chunked attention."""
+    from dlm_b200.models.zasazen import layer_order
+    runs = len(layer_order(len(z["layers"]), z.get("loop")))
+    left = z["layers"][-1]["mixer"]["left"]
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=runs, hidden_size=z["width"],
+                num_attention_heads=left["heads"], num_key_value_heads=left["kv_heads"], head_dim=left["dim"],
+                num_experts=0, intermediate_size=z["layers"][0]["mlp"]["ff"], vocab_size=z["vocab"], rope_theta=1e6,
+                rms_norm_eps=1e-6, use_sliding_window=False, tie_word_embeddings=True, max_position_embeddings=8192)
+
+
+def salolorn_kernels(z, pk, batch, context, prefill_tokens):
+    """Each kernel of the design alone at the layer sizes of `z`, beside the like kernel of an existing model at the
+    same sizes: a prompt of `prefill_tokens` tokens of one request, and a decode step of `batch` requests at `context`
+    tokens.  Microseconds (median of 5, the cache flushed before each), the bytes the kernel has to move at least,
+    and that over time over the measured copy bandwidth; the attentions also with their flops."""
+    import math
+    from types import SimpleNamespace
+
+    import torch
+
+    from dlm_b200.ops import native_ops
+    ops = native_ops(fast=True)
+    dev = "cuda"
+    W = z["width"]
+    md = next(L["mixer"] for L in z["layers"] if L["type"] == "delta")
+    ml = next(L["mixer"] for L in z["layers"] if L["type"] == "latent_attention")
+    pair = next(L["mixer"] for L in z["layers"] if L["type"] == "parallel")
+    lf, rt = pair["left"], pair["right"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    bf = torch.bfloat16
+    rows = {}
+
+    def timed(name, case, fn, nbytes, flop=None):
+        ts = []
+        for _ in range(6):
+            _flush(torch, flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        us = statistics.median(ts[1:]) * 1e3
+        row = {"us": round(us, 1), "mbytes": round(nbytes / 1e6, 2),
+               "frac_of_copy": round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)}
+        if flop is not None:
+            row["gflop"] = round(flop / 1e9, 2)
+            row["frac_of_bf16_peak"] = round(flop / (us * 1e-6) / (pk["bf16_tflops"] * 1e12), 4)
+        rows.setdefault(name, {})[case] = row
+
+    for case, lens, start in (("prefill", [prefill_tokens], 0), ("decode", [1] * batch, context)):
+        T, R = sum(lens), len(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        b = SimpleNamespace(num_requests=R, cu_q=torch.tensor(cu, **i32), state_slot=torch.arange(R, **i32),
+                            token_req=torch.tensor([r for r, n in enumerate(lens) for _ in range(n)], **i32),
+                            positions=torch.tensor([start + i for n in lens for i in range(n)], **i32))
+        held = start + max(lens)
+        b.max_kv_len = held
+        pages_each = -(-held // 64)
+        table = torch.arange(R * pages_each, **i32).reshape(R, pages_each)
+        slots = torch.cat([table[r, (start + torch.arange(n, device=dev)) // 64] * 64 + (start + torch.arange(n, device=dev)) % 64
+                           for r, n in enumerate(lens)]).to(torch.int32)
+        kv_len = torch.tensor([start + n for n in lens], **i32)
+        single = sum(1 for n in lens if n == 1)
+        # ---- delta rule: convolutions, the recurrence, the norm per head with its gate
+        H, G, d, dv, taps = md["heads"], md["kv_heads"], md["dim"], md["vdim"], md["conv"]
+        C = 2 * G * d + H * dv
+        proj = torch.randn(T, C + 2 * H + H * dv, device=dev)
+        cw = torch.randn(C, taps, device=dev) * 0.5
+        cst = torch.zeros(R + 1, taps - 1, C, device=dev)
+        timed("causal_conv + silu (q, k, v of the delta rule)", case,
+              lambda: ops.causal_conv(proj[:, :C], cw, None, cst, b, False, True, torch.float32),
+              T * C * 8 + 2 * R * (taps - 1) * C * 4)
+        qkv = ops.causal_conv(proj[:, :C], cw, None, cst, b, False, True, torch.float32)
+        A_log, dtb = torch.rand(H, device=dev) - 1.0, torch.randn(H, device=dev)
+        dst = torch.zeros(R + 1, H, d, dv, device=dev)
+        timed("gated_scan, delta rule with a decay per head", case,
+              lambda: ops.gated_scan(qkv[:, :G * d], qkv[:, G * d:2 * G * d], qkv[:, 2 * G * d:], proj[:, C + H:C + 2 * H],
+                                     proj[:, C:C + H], dst, b, H, G, d, dv, unit_eps=1e-6, q_scale=d ** -0.5, A_log=A_log,
+                                     decay_bias=dtb),
+              T * (2 * G * d + 2 * H * dv + 2 * H) * 4 + 2 * R * H * d * dv * 4)
+        Hz, dz = W // 64, 64                                       # Zesapel's delta rule at the same width
+        HD = Hz * dz
+        zproj, lw, ab = torch.randn(T, 5 * HD + 16, device=dev), torch.randn(T, HD, device=dev), torch.zeros(HD, device=dev)
+        zst = torch.zeros(R + 1, Hz, dz, dz, device=dev)
+        timed("delta_scan (Zesapel's delta rule, 64 x 64 heads)", case,
+              lambda: ops.delta_scan(zproj, (0, HD, 2 * HD, 3 * HD), lw, ab, zst, b, Hz, dz, 1e-6, math.exp(-0.5)),
+              T * HD * 6 * 4 + 2 * R * Hz * dz * dz * 4)
+        o_ = torch.randn(T, H * dv, device=dev)
+        nw = torch.randn(H * dv, device=dev)
+        timed("gated_rmsnorm (per head, silu gate)", case,
+              lambda: ops.gated_rmsnorm(o_, proj[:, C + 2 * H:], nw, H, 1e-6, "silu_after", bf), T * H * dv * 10)
+        # ---- linear attention with a decay per key channel, beside the recurrence with constant decays
+        H2, d2, dv2 = rt["heads"], rt["dim"], rt["vdim"]
+        gp = torch.randn(T, 3 * H2 * d2 + H2 * dv2, device=dev)
+        gst = torch.zeros(R + 1, H2, d2, dv2, device=dev)
+        timed("gated_scan, decay per key channel", case,
+              lambda: ops.gated_scan(gp[:, :H2 * d2], gp[:, H2 * d2:2 * H2 * d2], gp[:, 3 * H2 * d2:], gp[:, 2 * H2 * d2:3 * H2 * d2],
+                                     None, gst, b, H2, H2, d2, dv2, q_scale=d2 ** -0.5, tau=rt["tau"]),
+              T * (3 * H2 * d2 + 2 * H2 * dv2) * 4 + 2 * R * H2 * d2 * dv2 * 4)
+        rp = torch.randn(T, H2 * dv2 + 2 * H2 * d2, device=dev)
+        decay = torch.tensor([1.0 - 2.0 ** (-5 - 5 * i / max(H2 - 1, 1)) for i in range(H2)], device=dev)
+        rst = torch.zeros(R + 1, H2, d2, dv2, device=dev)
+        timed("ssm_scan with constant decays (Zasazen's retention)", case,
+              lambda: ops.ssm_scan(rp, None, None, None, None, rst, b, H2, dv2, d2, H2, fixed_decay=decay),
+              T * (H2 * dv2 * 2 + 2 * H2 * d2) * 4 + 2 * R * H2 * d2 * dv2 * 4)
+        # ---- attention inside chunks with a sink and a gate, beside the plain causal attention
+        Ha, Ga, da, dva = lf["heads"], lf["kv_heads"], lf["dim"], lf["vdim"]
+        D = max(da, dva)
+        chunk = lf["mask"]["size"]
+        k_cache = (torch.randn(R * pages_each + 1, Ga, 64, D, device=dev) * 0.3).to(bf)
+        v_cache = (torch.randn(R * pages_each + 1, Ga, 64, D, device=dev) * 0.3).to(bf)
+        aq = torch.randn(T, (Ha + Ga) * da + Ga * dva + Ha, device=dev)
+        qn, kn = torch.randn(da, device=dev), torch.randn(da, device=dev)
+        freq = torch.tensor([1e6 ** (-2.0 * i / da) for i in range(da // 2)], device=dev)
+        io = T * ((Ha + Ga) * da + Ga * dva) * 4 + T * (Ha + 2 * Ga) * D * 2
+        timed("head_norm_rope_write", case,
+              lambda: ops.head_norm_rope_write(aq, b.positions, qn, kn, 1e-6, freq, da, False, slots, k_cache, v_cache, Ha,
+                                               Ga, da, dva, D, bf), io)
+        pq = torch.randn(T, (Ha + 2 * Ga) * D, device=dev)
+        timed("rope_kv_write (Qwen2's)", case,
+              lambda: ops.rope_kv_write(pq, b.positions, freq, D, slots, k_cache, v_cache, Ha, Ga, D, bf), io)
+        q = ops.head_norm_rope_write(aq, b.positions, qn, kn, 1e-6, freq, da, False, slots, k_cache, v_cache, Ha, Ga, da,
+                                     dva, D, bf)
+        sinks = torch.randn(Ha, device=dev)
+        seen = [(start + i) % chunk + 1 for n in lens for i in range(n)]       # keys a query meets inside its chunk
+        for name, ch, sk, keys, span in (
+                ("attention inside chunks with a sink", chunk, sinks, sum(seen), min(chunk, held)),
+                ("attention, causal (Qwen2's)", 0, None, sum(start + i + 1 for n in lens for i in range(n)), held)):
+            nbytes = (R * max(seen) if (case == "decode" and ch) else (R if case == "decode" else 1) * span) * Ga * D * 4 \
+                + T * Ha * D * 4
+            timed(name, case, lambda: ops.attention(q, k_cache, v_cache, table, b.cu_q, kv_len, 0, 0.125, Ha, Ga, D, max(lens),
+                                                    held, single, chunk=ch, sinks=sk), nbytes, flop=4.0 * keys * Ha * D)
+        o2 = torch.randn(T, Ha * D, device=dev).to(bf)
+        timed("head_gate", case, lambda: ops.head_gate(o2, aq[:, (Ha + Ga) * da + Ga * dva:], Ha, D, 1.0), T * Ha * D * 4)
+        # ---- latent attention: direct queries, neighbour pairs, no window and no sink
+        Hl, dn, dr, dvl, rank = ml["heads"], ml["dim"], ml["rot_dim"], ml["vdim"], ml["kv_rank"]
+        cache = (torch.randn(R * pages_each + 1, 1, 64, rank + dr, device=dev) * 0.3).to(bf)
+        lp = torch.randn(T, Hl * (dn + dr) + rank + dr, device=dev)
+        kvn = torch.randn(rank, device=dev)
+        lfreq = torch.tensor([10000.0 ** (-2.0 * i / dr) for i in range(dr // 2)], device=dev)
+        qc = Hl * (dn + dr)
+        timed("latent_prep (norm, rotation, cache write)", case,
+              lambda: ops.latent_prep(lp, 0, 0, None, qc, rank, kvn, dr, lfreq, dr, b.positions, slots, 1e-6, cache, bf,
+                                      interleaved=True), T * (rank + dr) * 6)
+        wukT = (torch.randn(Hl, rank, dn, device=dev) * 0.05).to(bf)
+        wuv = (torch.randn(Hl, dvl, rank, device=dev) * 0.05).to(bf)
+        offs = ops.head_offsets(Hl, T, dev)
+        lq = lp[:, :qc]
+        qpl, q_rot = ops.latent_q_split(lq, b.positions, lfreq, dr, Hl, dn, dr, bf, interleaved=True)
+        q_lat = ops.grouped_linear(qpl.reshape(Hl * T, dn), wukT, offs).reshape(Hl, T, rank)
+        lat = ops.latent_attention(q_lat, q_rot, None, cache, table, b, Hl, dr, rank, 0, 0.07)
+        val = ops.grouped_linear(lat.reshape(Hl * T, rank), wuv, offs)
+        timed("latent_q_split (neighbour pairs)", case,
+              lambda: ops.latent_q_split(lq, b.positions, lfreq, dr, Hl, dn, dr, bf, interleaved=True),
+              T * Hl * ((dn + dr) * 4 + dn * 2 + dr * 4))
+        timed("queries through W_uk (grouped product)", case,
+              lambda: ops.grouped_linear(qpl.reshape(Hl * T, dn), wukT, offs), Hl * (T * dn * 2 + rank * dn * 2 + T * rank * 4))
+        zero_sink = torch.zeros(Hl, device=dev)
+        for name, win, sk in (("latent_attention, all keys, no sink", 0, None),
+                              ("latent_attention, window 1024 and a sink (Zesapel's)", 1024, zero_sink)):
+            keys = sum(min(win or 10 ** 9, start + i + 1) for n in lens for i in range(n))
+            span = min(win or held, held)
+            timed(name, case, lambda: ops.latent_attention(q_lat, q_rot, sk, cache, table, b, Hl, dr, rank, win, 0.07),
+                  (R * span if case == "decode" else held) * (rank + dr) * 2 + T * Hl * (rank * 6 + dr * 4),
+                  flop=2.0 * keys * Hl * (2 * rank + dr))
+        timed("latents through W_uv (grouped product)", case,
+              lambda: ops.grouped_linear(lat.reshape(Hl * T, rank), wuv, offs), Hl * (T * rank * 2 + rank * dvl * 2 + T * dvl * 4))
+        timed("latent_gate_out (no gate)", case, lambda: ops.latent_gate_out(val, None, Hl, dvl, bf), T * Hl * dvl * 6)
+        # ---- norms on both sides of a sublayer, the pass entry
+        resid, y, x0 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+        wv = torch.randn(W, device=dev)
+        timed("norm_add_norm (closing norm, add, opening norm)", case,
+              lambda: ops.norm_add_norm(resid, y, wv, wv, 1e-6, bf), T * W * 14)
+        timed("rmsnorm (Qwen2's opening norm)", case, lambda: ops.rmsnorm(resid, wv, 1e-6, bf), T * W * 6)
+        timed("add_vec_rows (pass entry)", case, lambda: ops.add_vec_rows(resid, x0, wv), T * W * 12)
+    ops.check_errors()
+    return rows
+
+
+def run_salolorn(args, pk) -> dict:
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    out = {"workload": "salolorn", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+           "peaks": pk, "sizes": {}, "l2": "a buffer larger than L2 is written before every timed step"}
+    for width in (1024, 2048, 4096):
+        z = salolorn_config(width)
+        q = qwen_config_like_salolorn(z)
+        out["sizes"][str(width)] = {
+            "layer_runs": q["num_hidden_layers"], "salolorn": measure_engine(z, args.batch, args.prompt_len, args.steps, 2048),
+            "qwen2_dense": measure_engine(q, args.batch, args.prompt_len, args.steps, 2048)}
+    out["kernels_width_2048"] = salolorn_kernels(salolorn_config(2048), pk, args.batch, args.prompt_len, 2048)
+    t1 = time.time()
+    time.sleep(0.2)
+    sampler.stop()
+    out["clocks"] = sampler.summary(t0, t1)
+    return out
+
+
 def layers_that_fit(raw, want, reserve_gb=40.0):
     """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
     the cache pool, the head, graphs and activations."""
@@ -946,7 +1172,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel", "zasazen"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel", "zasazen", "salolorn"],
                     help="serving: the continuous-batching workload on the windowed model, instead of the default line; "
                          "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own; "
                          "kernels: the weight-streaming product alone")
@@ -982,6 +1208,9 @@ def main() -> int:
         return 0
     if args.workload == "zasazen":
         print(json.dumps(run_zasazen(args, pk)))
+        return 0
+    if args.workload == "salolorn":
+        print(json.dumps(run_salolorn(args, pk)))
         return 0
     max_batch = 64 if not args.no_points else args.batch
     m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk, page=args.page_size)

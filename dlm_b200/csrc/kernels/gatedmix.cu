@@ -12,61 +12,121 @@ namespace {
 
 __device__ __forceinline__ float sigmoid_g(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_g(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+// One 32-bit word from global to shared memory without holding a register for it; the thread that issued the copy
+// sees it after copy_async_wait_all(), the others after the block's next barrier.
+__device__ __forceinline__ void copy_async4(float* smem_dst, const float* gmem_src) {
+    const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------------ gated scan
 // Per head, S [dk, dv] in 32-bit:  S <- diag(a) S;  u = DELTA ? beta (v - S^T k) : v;  S <- S + k u^T;  o = S^T q.
-// A block owns (head, request, a run of value columns).  Column j of S is shared by `parts` neighbouring lanes;
-// lane `part` keeps rows part, part + parts, ... in registers.  S^T k and S^T q are added per lane and meet in a
-// butterfly of shuffles, so the order of every sum is fixed by dk alone and a request's result does not depend on
-// how its tokens were cut into steps.  Tokens are staged in tiles: a warp per token loads q and k, takes their
-// lengths when they are to be unit vectors, and turns the raw decay and write strength into factors; then every
-// thread walks the tile's tokens in order.
-template <int NPT, bool DELTA>
+// A block owns (head, request, a run of value columns).  Column j of S is shared by PARTS neighbouring lanes; a
+// lane keeps NG groups of four neighbouring rows in registers (group ig * PARTS + part), so that q, k and the decays
+// of its rows come from shared memory as 128-bit loads.  Rows beyond dk (up to 4 NG PARTS) are zeros with a decay
+// of one and change nothing.  S^T k and S^T q are added per lane and meet in a butterfly of shuffles, so the order
+// of every sum is fixed by dk alone and a request's result does not depend on how its tokens were cut into steps.
+// Tokens are staged in tiles in two buffers: while every thread walks one tile's tokens in order, asynchronous
+// copies bring the next tile's raw values; a warp per token then takes the lengths of q and k when they are to be
+// unit vectors and turns the raw decay and write strength into factors.
+template <int NG, int PARTS, bool DELTA>
 __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                                   const float* __restrict__ v, int ldv, const float* __restrict__ dec, int ldd,
                                   const float* __restrict__ beta, int ldb, const float* __restrict__ A_log,
                                   const float* __restrict__ dec_bias, float* state,
                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
                                   int ldo, int heads, int qk_heads, int dk, int dv, int unit, float unit_eps,
-                                  float q_scale, int decay_kind, float inv_tau, int parts, int tile) {
+                                  float q_scale, int decay_kind, float inv_tau, int tile) {
     dep_wait();
-    extern __shared__ __align__(16) float sm[];           // [tile][3 dk + cols + 1]: q, k, a, v, beta
+    constexpr int DKP = 4 * NG * PARTS;                   // rows as the block keeps them
+    extern __shared__ __align__(16) float sm[];           // 2 x [tile][q: DKP | k: DKP | a: DKP (a decay per channel) | v | a0, beta]
     const int h = blockIdx.x, r = blockIdx.y;
-    const int cols = blockDim.x / parts;
-    const int part = threadIdx.x % parts, col = threadIdx.x / parts;
+    const int cols = blockDim.x / PARTS;
+    const int colsp = (cols + 3) & ~3;
+    const int part = threadIdx.x % PARTS, col = threadIdx.x / PARTS;
     const int j0 = blockIdx.z * cols;
     const int j = j0 + col;
     const bool live = j < dv;
     const int ncols = min(cols, dv - j0);
-    const int rl = 3 * dk + cols + 1;
+    const int off_v = (decay_kind == 0 ? 2 : 3) * DKP, off_s = off_v + colsp;
+    const int rl = off_s + 4;
     const int hq = h / (heads / qk_heads);
     float* st = state + ((long long)state_slot[r] * heads + h) * dk * dv;
-    float s[NPT];
+    float s[4 * NG];
 #pragma unroll
-    for (int ii = 0; ii < NPT; ++ii) {
-        const int i = part + parts * ii;
-        s[ii] = (live && i < dk) ? st[(long long)i * dv + j] : 0.f;
-    }
+    for (int ig = 0; ig < NG; ++ig)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = 4 * (ig * PARTS + part) + e;
+            s[4 * ig + e] = (live && i < dk) ? st[(long long)i * dv + j] : 0.f;
+        }
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const float neg_rate = decay_kind == 0 ? -expf(A_log[h]) : 0.f;
     const float bias0 = (decay_kind == 0 && dec_bias != nullptr) ? dec_bias[h] : 0.f;
-    for (int first = t0; first < t1; first += tile) {
+    // Copies of a tile's raw values into one of the two buffers, without waiting: a warp a token, a lane the same
+    // entries that it finishes later, so that a lane waits for its own copies only.
+    auto fetch = [&](int first, float* buf) {
         const int n = min(tile, t1 - first);
-        __syncthreads();                                   // the walk before has left the buffer
         for (int tok = warp; tok < n; tok += nwarp) {
             const long long t = first + tok;
-            float* row = sm + (size_t)tok * rl;
+            float* row = buf + (size_t)tok * rl;
             const float* qsrc = q + t * ldq + hq * dk;
             const float* ksrc = k + t * ldk + hq * dk;
-            float sq = 0.f, sk = 0.f;
-            for (int i = lane; i < dk; i += 32) {
-                const float qv = qsrc[i], kv = ksrc[i];
-                row[i] = qv;
-                row[dk + i] = kv;
-                sq = fmaf(qv, qv, sq);
-                sk = fmaf(kv, kv, sk);
+#pragma unroll
+            for (int i = lane; i < DKP; i += 32) {
+                if (i < dk) {
+                    copy_async4(row + i, qsrc + i);
+                    copy_async4(row + DKP + i, ksrc + i);
+                } else {
+                    row[i] = 0.f;
+                    row[DKP + i] = 0.f;
+                }
             }
+            const float* vsrc = v + t * ldv + h * dv + j0;
+            for (int c = lane; c < ncols; c += 32) copy_async4(row + off_v + c, vsrc + c);
+            if (decay_kind == 0) {
+                if (lane == 0) copy_async4(row + off_s, dec + t * ldd + h);
+            } else {
+                const float* dsrc = dec + t * ldd + h * dk;
+#pragma unroll
+                for (int i = lane; i < DKP; i += 32)
+                    if (i < dk) copy_async4(row + 2 * DKP + i, dsrc + i);
+            }
+            if (DELTA && lane == 1) copy_async4(row + off_s + 1, beta + t * ldb + h);
+        }
+        copy_async_commit();
+    };
+    float* const buf0 = sm;
+    float* const buf1 = sm + (size_t)tile * rl;
+    if (t0 < t1) fetch(t0, buf0);
+    int which = 0;
+    for (int first = t0; first < t1; first += tile, which ^= 1) {
+        const int n = min(tile, t1 - first);
+        float* const cur = which ? buf1 : buf0;
+        copy_async_wait_all();
+        for (int tok = warp; tok < n; tok += nwarp) {      // lengths, decays and write strengths of the tile
+            float* row = cur + (size_t)tok * rl;
+            float qv[DKP / 32 > 0 ? DKP / 32 : 1], kv[DKP / 32 > 0 ? DKP / 32 : 1];
+            float sq = 0.f, sk = 0.f;
+#pragma unroll
+            for (int ii = 0; ii * 32 < DKP; ++ii) {
+                const int i = lane + 32 * ii;
+                qv[ii] = i < DKP ? row[i] : 0.f;
+                kv[ii] = i < DKP ? row[DKP + i] : 0.f;
+                sq = fmaf(qv[ii], qv[ii], sq);
+                sk = fmaf(kv[ii], kv[ii], sk);
+            }
+            if (decay_kind == 0) {
+                if (lane == 0) row[off_s] = expf(neg_rate * softplus_g(row[off_s] + bias0));
+            } else {
+#pragma unroll
+                for (int i = lane; i < DKP; i += 32)
+                    row[2 * DKP + i] = i < dk ? expf(-softplus_g(-row[2 * DKP + i]) * inv_tau) : 1.0f;
+            }
+            if (lane == 1) row[off_s + 1] = DELTA ? sigmoid_g(row[off_s + 1]) : 0.f;
             float fq = q_scale, fk = 1.0f;
             if (unit) {
                 sq = warp_sum(sq);
@@ -74,62 +134,81 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                 fq = q_scale * (1.0f / sqrtf(sq + unit_eps));
                 fk = 1.0f / sqrtf(sk + unit_eps);
             }
-            for (int i = lane; i < dk; i += 32) {
-                row[i] *= fq;
-                row[dk + i] *= fk;
-            }
-            if (decay_kind == 0) {
-                if (lane == 0) row[2 * dk] = expf(neg_rate * softplus_g(dec[t * ldd + h] + bias0));
-            } else {
-                const float* dsrc = dec + t * ldd + h * dk;
-                for (int i = lane; i < dk; i += 32) row[2 * dk + i] = expf(-softplus_g(-dsrc[i]) * inv_tau);
-            }
-            const float* vsrc = v + t * ldv + h * dv + j0;
-            for (int c = lane; c < ncols; c += 32) row[3 * dk + c] = vsrc[c];
-            if (lane == 0) row[3 * dk + cols] = DELTA ? sigmoid_g(beta[t * ldb + h]) : 0.f;
-        }
-        __syncthreads();
-        for (int tok = 0; tok < n; ++tok) {
-            const float* row = sm + (size_t)tok * rl;
-            const float a0 = row[2 * dk];
-            float kk[NPT], ksum = 0.f;
 #pragma unroll
-            for (int ii = 0; ii < NPT; ++ii) {
-                const int i = part + parts * ii;
-                kk[ii] = 0.f;
-                if (i < dk) {
-                    s[ii] *= decay_kind == 0 ? a0 : row[2 * dk + i];
-                    kk[ii] = row[dk + i];
-                    if (DELTA) ksum = fmaf(kk[ii], s[ii], ksum);
+            for (int ii = 0; ii * 32 < DKP; ++ii) {
+                const int i = lane + 32 * ii;
+                if (i < DKP) {
+                    row[i] = qv[ii] * fq;
+                    row[DKP + i] = kv[ii] * fk;
                 }
             }
-            float u = live ? row[3 * dk + col] : 0.f;
+        }
+        __syncthreads();                                   // the tile is ready, and the walk before has left the other buffer
+        if (first + tile < t1) fetch(first + tile, which ? buf0 : buf1);
+        const float* const sm_cur = cur;
+#pragma unroll 2
+        for (int tok = 0; tok < n; ++tok) {
+            const float* row = sm_cur + (size_t)tok * rl;
+            const float4* q4 = reinterpret_cast<const float4*>(row);
+            const float4* k4 = reinterpret_cast<const float4*>(row + DKP);
+            const float4* a4 = reinterpret_cast<const float4*>(row + 2 * DKP);
+            const float2 sc = *reinterpret_cast<const float2*>(row + off_s);      // decay of the head, write strength
+            float4 kk[NG];
+            float ksum = 0.f;
+#pragma unroll
+            for (int ig = 0; ig < NG; ++ig) {
+                const int g = ig * PARTS + part;
+                kk[ig] = k4[g];
+                if (decay_kind == 0) {
+                    s[4 * ig] *= sc.x; s[4 * ig + 1] *= sc.x; s[4 * ig + 2] *= sc.x; s[4 * ig + 3] *= sc.x;
+                } else {
+                    const float4 a = a4[g];
+                    s[4 * ig] *= a.x; s[4 * ig + 1] *= a.y; s[4 * ig + 2] *= a.z; s[4 * ig + 3] *= a.w;
+                }
+                if (DELTA) {
+                    float p = kk[ig].x * s[4 * ig];
+                    p = fmaf(kk[ig].y, s[4 * ig + 1], p);
+                    p = fmaf(kk[ig].z, s[4 * ig + 2], p);
+                    p = fmaf(kk[ig].w, s[4 * ig + 3], p);
+                    ksum += p;
+                }
+            }
+            float u = live ? row[off_v + col] : 0.f;
             if (DELTA) {
-                for (int x = parts >> 1; x > 0; x >>= 1) ksum += __shfl_xor_sync(0xffffffffu, ksum, x);
-                u = row[3 * dk + cols] * (u - ksum);
+#pragma unroll
+                for (int x = PARTS >> 1; x > 0; x >>= 1) ksum += __shfl_xor_sync(0xffffffffu, ksum, x);
+                u = sc.y * (u - ksum);
             }
             float acc = 0.f;
 #pragma unroll
-            for (int ii = 0; ii < NPT; ++ii) {
-                const int i = part + parts * ii;
-                if (i < dk) {
-                    s[ii] = fmaf(kk[ii], u, s[ii]);
-                    acc = fmaf(row[i], s[ii], acc);
-                }
+            for (int ig = 0; ig < NG; ++ig) {
+                const float4 qq = q4[ig * PARTS + part];
+                s[4 * ig] = fmaf(kk[ig].x, u, s[4 * ig]);
+                s[4 * ig + 1] = fmaf(kk[ig].y, u, s[4 * ig + 1]);
+                s[4 * ig + 2] = fmaf(kk[ig].z, u, s[4 * ig + 2]);
+                s[4 * ig + 3] = fmaf(kk[ig].w, u, s[4 * ig + 3]);
+                float p = qq.x * s[4 * ig];
+                p = fmaf(qq.y, s[4 * ig + 1], p);
+                p = fmaf(qq.z, s[4 * ig + 2], p);
+                p = fmaf(qq.w, s[4 * ig + 3], p);
+                acc += p;
             }
-            for (int x = parts >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
+#pragma unroll
+            for (int x = PARTS >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
             if (live && part == 0) o[(long long)(first + tok) * ldo + h * dv + j] = acc;
         }
     }
 #pragma unroll
-    for (int ii = 0; ii < NPT; ++ii) {
-        const int i = part + parts * ii;
-        if (live && i < dk) st[(long long)i * dv + j] = s[ii];
-    }
+    for (int ig = 0; ig < NG; ++ig)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = 4 * (ig * PARTS + part) + e;
+            if (live && i < dk) st[(long long)i * dv + j] = s[4 * ig + e];
+        }
 }
 
 // ------------------------------------------------------------------- per-head norms, rotation, paged write
-// One block a token, a warp a head.  x <- (x / sqrt(mean x^2 + eps)) * w over the head's d entries (w shared by
+// A warp a head: block (t, y) takes heads y * warps .. of token t.  x <- (x / sqrt(mean x^2 + eps)) * w over the head's d entries (w shared by
 // the heads; nullptr: no norm), then the first rot_dims entries are rotated by position * inv_freq[pair]; q goes
 // to q_out, k and v to the token's slot of the paged caches, every head D wide with zeros beyond its own size.
 template <typename T>
@@ -152,7 +231,7 @@ __global__ void head_norm_rope_write_kernel(const float* qkv, int ld, const int3
         slot = -1;
     }
     const long long page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-    for (int hh = warp; hh < nh + 2 * nkv; hh += nwarp) {
+    for (int hh = blockIdx.y * nwarp + warp; hh < nh + 2 * nkv; hh += gridDim.y * nwarp) {
         if (hh >= nh + nkv) {                               // a value head: copied as it is
             if (slot < 0) continue;
             const int g = hh - nh - nkv;
@@ -260,33 +339,36 @@ void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v
     DLM_CHECK(decay_kind == 0 || decay_kind == 1, "gated_scan: decay kind 0 (per head) or 1 (per key channel)");
     DLM_CHECK(decay_kind == 1 || A_log != nullptr, "gated_scan: a decay per head needs its rates");
     DLM_CHECK(decay_kind == 0 || tau > 0.f, "gated_scan: tau must be positive");
-    int parts = 1;
-    const int want = dk > 64 ? 8 : 4;                        // rows a lane: short chains for small heads
-    while (parts < 32 && (dk + parts - 1) / parts > want) parts *= 2;
-    const int per = (dk + parts - 1) / parts;
+    // rows a lane keeps: 4 NG, over PARTS lanes a column (short chains for small heads)
+    const int ng = dk <= 64 ? 1 : (dk <= 256 ? 2 : 4);
+    const int parts = dk <= 16 ? 4 : (dk <= 32 ? 8 : (dk <= 128 ? 16 : 32));
+    const int dkp = 4 * ng * parts;
     int cols = (parts >= 16 ? 256 : 128) / parts;
     while (cols > 1 && cols / 2 >= dv) cols /= 2;           // no more columns than the head has (a power of two)
     if (cols * parts < 32) cols = 32 / parts;                // at least a warp
     const int chunks = (dv + cols - 1) / cols;
-    const int rl = 3 * dk + cols + 1;
-    int tile = (40 * 1024) / (rl * (int)sizeof(float));
+    const int rl = (decay_kind == 0 ? 2 : 3) * dkp + ((cols + 3) & ~3) + 4;
+    int tile = (23 * 1024) / (rl * (int)sizeof(float));     // two buffers within 48 KB
     tile = tile < 1 ? 1 : (tile > 32 ? 32 : tile);
-    const size_t smem = (size_t)tile * rl * sizeof(float);
+    const size_t smem = (size_t)2 * tile * rl * sizeof(float);
     const dim3 grid(heads, R, chunks);
     const float inv_tau = decay_kind == 1 ? 1.0f / tau : 0.f;
-#define DLM_GSCAN(NPT, DELTA)                                                                                       \
-    gated_scan_kernel<NPT, DELTA><<<grid, cols * parts, smem, stream>>>(q, ldq, k, ldk, v, ldv, dec, ldd, beta, ldb,  \
-        A_log, dec_bias, state, cu_q, state_slot, o, ldo, heads, qk_heads, dk, dv, unit, unit_eps, q_scale,         \
-        decay_kind, inv_tau, parts, tile)
-    if (beta != nullptr) {
-        if (per <= 4) DLM_GSCAN(4, true);
-        else if (per <= 8) DLM_GSCAN(8, true);
-        else DLM_GSCAN(16, true);
-    } else {
-        if (per <= 4) DLM_GSCAN(4, false);
-        else if (per <= 8) DLM_GSCAN(8, false);
-        else DLM_GSCAN(16, false);
-    }
+#define DLM_GSCAN(NG, PARTS, DELTA)                                                                                 \
+    gated_scan_kernel<NG, PARTS, DELTA><<<grid, cols * parts, smem, stream>>>(q, ldq, k, ldk, v, ldv, dec, ldd,     \
+        beta, ldb, A_log, dec_bias, state, cu_q, state_slot, o, ldo, heads, qk_heads, dk, dv, unit, unit_eps,       \
+        q_scale, decay_kind, inv_tau, tile)
+#define DLM_GSCAN_SIZES(DELTA)                                                                                      \
+    do {                                                                                                            \
+        if (dkp == 16) DLM_GSCAN(1, 4, DELTA);                                                                      \
+        else if (dkp == 32) DLM_GSCAN(1, 8, DELTA);                                                                 \
+        else if (dkp == 64) DLM_GSCAN(1, 16, DELTA);                                                                \
+        else if (dkp == 128) DLM_GSCAN(2, 16, DELTA);                                                               \
+        else if (dkp == 256) DLM_GSCAN(2, 32, DELTA);                                                               \
+        else DLM_GSCAN(4, 32, DELTA);                                                                               \
+    } while (0)
+    if (beta != nullptr) DLM_GSCAN_SIZES(true);
+    else DLM_GSCAN_SIZES(false);
+#undef DLM_GSCAN_SIZES
 #undef DLM_GSCAN
     check_launch("gated_scan");
 }
@@ -300,12 +382,14 @@ void head_norm_rope_write(const float* qkv, int ld, const int32_t* positions, co
     DLM_CHECK(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= d, "head_norm_rope_write: rotated dims must be even and <= d");
     DLM_CHECK(rot_dims == 0 || inv_freq != nullptr, "head_norm_rope_write: a rotation needs its table");
     int* err = error_flag_ptr();
+    const int warps = 4;
+    const dim3 grid(T, (nh + 2 * nkv + warps - 1) / warps);
     if (dtype == F32)
-        launch_dep(head_norm_rope_write_kernel<float>, dim3(T), dim3(128), 0, stream, qkv, ld, positions, qn_w, kn_w, eps,
+        launch_dep(head_norm_rope_write_kernel<float>, grid, dim3(32 * warps), 0, stream, qkv, ld, positions, qn_w, kn_w, eps,
                    inv_freq, rot_dims, interleaved, slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
                    static_cast<float*>(v_cache), nh, nkv, d, dv, D, page_size, total_pages, err);
     else
-        launch_dep(head_norm_rope_write_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, qkv, ld, positions, qn_w,
+        launch_dep(head_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(32 * warps), 0, stream, qkv, ld, positions, qn_w,
                    kn_w, eps, inv_freq, rot_dims, interleaved, slots, static_cast<__nv_bfloat16*>(q_out),
                    static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), nh, nkv, d, dv, D,
                    page_size, total_pages, err);
