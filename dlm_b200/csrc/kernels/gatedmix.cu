@@ -208,18 +208,21 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
 }
 
 // ------------------------------------------------------------------- per-head norms, rotation, paged write
-// A warp a head: block (t, y) takes heads y * warps .. of token t.  x <- (x / sqrt(mean x^2 + eps)) * w over the head's d entries (w shared by
-// the heads; nullptr: no norm), then the first rot_dims entries are rotated by position * inv_freq[pair]; q goes
-// to q_out, k and v to the token's slot of the paged caches, every head D wide with zeros beyond its own size.
+// A warp a head: block (t, y) takes heads y * warps .. of token t.  x <- (x / sqrt(mean x^2 + eps)) * w over the
+// head's d entries (w shared by the heads; nullptr: no norm), kept in shared memory; then the first rot_dims entries
+// are rotated by position * inv_freq[pair], a lane a pair; q goes to q_out, k and v to the token's slot of the
+// paged caches, every head D wide with zeros beyond its own size.
 template <typename T>
-__global__ void head_norm_rope_write_kernel(const float* qkv, int ld, const int32_t* __restrict__ positions,
+__global__ void head_norm_rope_write_kernel(const float* __restrict__ qkv, int ld, const int32_t* __restrict__ positions,
                                             const float* __restrict__ qn_w, const float* __restrict__ kn_w, float eps,
                                             const float* __restrict__ inv_freq, int rot_dims, int interleaved,
-                                            const int32_t* __restrict__ slots, T* q_out, T* k_cache, T* v_cache,
-                                            int nh, int nkv, int d, int dv, int D, int page_size, int total_pages,
+                                            const int32_t* __restrict__ slots, T* __restrict__ q_out,
+                                            T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv, int d,
+                                            int dv, int D, int page_size, int total_pages,
                                             int* err) {
     dep_wait();
     dep_launch_next();
+    extern __shared__ __align__(16) float head_stage[];    // [warps][d], [2][half]
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const float* row = qkv + (long long)t * ld;
@@ -231,6 +234,9 @@ __global__ void head_norm_rope_write_kernel(const float* qkv, int ld, const int3
         slot = -1;
     }
     const long long page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    float* sincos = head_stage + nwarp * d;                // [2][half]: the token's sines and cosines, once a block
+    for (int f = threadIdx.x; f < half; f += blockDim.x) sincosf(pos * inv_freq[f], sincos + f, sincos + half + f);
+    __syncthreads();
     for (int hh = blockIdx.y * nwarp + warp; hh < nh + 2 * nkv; hh += gridDim.y * nwarp) {
         if (hh >= nh + nkv) {                               // a value head: copied as it is
             if (slot < 0) continue;
@@ -244,36 +250,30 @@ __global__ void head_norm_rope_write_kernel(const float* qkv, int ld, const int3
         if (!is_q && slot < 0) continue;
         const float* src = row + (long long)hh * d;        // q heads, then k heads, all d wide
         const float* w = is_q ? qn_w : kn_w;
-        float inv = 1.0f;
-        if (w != nullptr) {
-            float ss = 0.f;
-            for (int i = lane; i < d; i += 32) ss = fmaf(src[i], src[i], ss);
-            ss = warp_sum(ss);
-            inv = 1.0f / sqrtf(ss / (float)d + eps);
+        float* sh = head_stage + warp * d;                  // the head as it is after the norm
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            const float x = src[i];
+            sh[i] = x;
+            ss = fmaf(x, x, ss);
         }
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+            for (int i = lane; i < d; i += 32) sh[i] = (sh[i] * inv) * w[i];      // a lane rereads what it wrote
+        }
+        __syncwarp();
         T* dst = is_q ? q_out + ((long long)t * nh + hh) * D
                       : k_cache + ((page * nkv + (hh - nh)) * page_size + off) * D;
-        for (int i = lane; i < D; i += 32) {
-            float val = 0.f;
-            if (i < d) {
-                const float x = w != nullptr ? (src[i] * inv) * w[i] : src[i];
-                val = x;
-                if (i < 2 * half) {
-                    int pi, f;
-                    float sign;
-                    if (interleaved) {
-                        pi = i ^ 1; f = i >> 1; sign = (i & 1) ? 1.f : -1.f;
-                    } else {
-                        pi = i < half ? i + half : i - half; f = i < half ? i : i - half; sign = i < half ? -1.f : 1.f;
-                    }
-                    const float y = w != nullptr ? (src[pi] * inv) * w[pi] : src[pi];
-                    float sn, cs;
-                    sincosf(pos * inv_freq[f], &sn, &cs);
-                    val = x * cs + sign * (y * sn);
-                }
-            }
-            dst[i] = from_f32<T>(val);
+        for (int f = lane; f < half; f += 32) {             // a lane a pair
+            const int ia = interleaved ? 2 * f : f, ib = interleaved ? 2 * f + 1 : f + half;
+            const float x = sh[ia], y = sh[ib];
+            const float sn = sincos[f], cs = sincos[half + f];
+            dst[ia] = from_f32<T>(x * cs - y * sn);
+            dst[ib] = from_f32<T>(y * cs + x * sn);
         }
+        for (int i = 2 * half + lane; i < D; i += 32) dst[i] = from_f32<T>(i < d ? sh[i] : 0.f);
+        __syncwarp();                                       // the next head takes the same staging row
     }
 }
 
@@ -284,34 +284,99 @@ __global__ void head_gate_kernel(T* o, const float* gate, int ldg, int nh, int D
     dep_launch_next();
     const int t = blockIdx.x;
     T* row = o + (long long)t * nh * D;
-    for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {
-        const float g = factor * sigmoid_g(gate[(long long)t * ldg + idx / D]);
-        row[idx] = from_f32<T>(to_f32(row[idx]) * g);
+    constexpr int U = 4;
+    for (int i0 = threadIdx.x; i0 < nh * D; i0 += U * blockDim.x) {
+        float g[U], v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = i0 + u * blockDim.x;
+            g[u] = idx < nh * D ? gate[(long long)t * ldg + idx / D] : 0.f;
+            v[u] = idx < nh * D ? to_f32(row[idx]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = i0 + u * blockDim.x;
+            if (idx < nh * D) row[idx] = from_f32<T>(v[u] * (factor * sigmoid_g(g[u])));
+        }
     }
 }
 
-// resid[t] += (y[t] / rms(y[t])) * w_post;  then, with w_next, out[t] = (resid[t] / rms(resid[t])) * w_next
+// resid[t] += (y[t] / rms(y[t])) * w_post;  then, with w_next, out[t] = (resid[t] / rms(resid[t])) * w_next.
+// `staged`: the two rows are read from global memory once, side by side, and kept in shared memory ([2][H]) for the
+// later passes (a thread rereads only its own entries); otherwise the later passes read global memory again.
 template <typename T>
-__global__ void norm_add_norm_kernel(float* resid, const float* y, const float* __restrict__ w_post,
-                                     const float* __restrict__ w_next, float eps, T* out, int H) {
+__global__ void norm_add_norm_kernel(float* __restrict__ resid, const float* __restrict__ y,
+                                     const float* __restrict__ w_post, const float* __restrict__ w_next, float eps,
+                                     T* __restrict__ out, int H, int staged) {
     dep_wait();
     dep_launch_next();
     __shared__ float s_part[32];
-    const int t = blockIdx.x;
+    extern __shared__ __align__(16) float row_stage[];
+    constexpr int U = 4;                                   // loads in flight a thread; the sums keep their order
+    const int t = blockIdx.x, step = blockDim.x;
     const float* yr = y + (long long)t * H;
     float* xr = resid + (long long)t * H;
+    const float* ys = staged ? row_stage : yr;
+    float* xs = staged ? row_stage + H : xr;
     float part = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) part = fmaf(yr[i], yr[i], part);
+    for (int i0 = threadIdx.x; i0 < H; i0 += U * step) {
+        float yv[U], xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * step;
+            yv[u] = i < H ? yr[i] : 0.f;
+            xv[u] = (staged && i < H) ? xr[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * step;
+            if (i < H) {
+                if (staged) {
+                    row_stage[i] = yv[u];
+                    row_stage[H + i] = xv[u];
+                }
+                part = fmaf(yv[u], yv[u], part);
+            }
+        }
+    }
     const float inv = 1.0f / sqrtf(block_sum(part, s_part) / (float)H + eps);
     part = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float x = xr[i] + (yr[i] * inv) * w_post[i];
-        xr[i] = x;
-        part = fmaf(x, x, part);
+    for (int i0 = threadIdx.x; i0 < H; i0 += U * step) {
+        float yv[U], xv[U], wv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * step;
+            yv[u] = i < H ? ys[i] : 0.f;
+            xv[u] = i < H ? xs[i] : 0.f;
+            wv[u] = i < H ? w_post[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * step;
+            if (i < H) {
+                const float x = xv[u] + (yv[u] * inv) * wv[u];
+                xs[i] = x;
+                if (staged) xr[i] = x;
+                part = fmaf(x, x, part);
+            }
+        }
     }
     if (w_next == nullptr) return;
     const float inv2 = 1.0f / sqrtf(block_sum(part, s_part) / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(long long)t * H + i] = from_f32<T>((xr[i] * inv2) * w_next[i]);
+    for (int i0 = threadIdx.x; i0 < H; i0 += U * step) {
+        float xv[U], wv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * step;
+            xv[u] = i < H ? xs[i] : 0.f;
+            wv[u] = i < H ? w_next[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * step;
+            if (i < H) out[(long long)t * H + i] = from_f32<T>((xv[u] * inv2) * wv[u]);
+        }
+    }
 }
 
 // x[t] += (x0 != nullptr ? x0[t] : 0) + vec
@@ -319,10 +384,21 @@ __global__ void add_vec_rows_kernel(float* x, const float* x0, const float* __re
     dep_wait();
     dep_launch_next();
     const long long base = (long long)blockIdx.x * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float a = x[base + i];
-        if (x0 != nullptr) a += x0[base + i];
-        x[base + i] = a + vec[i];
+    constexpr int U = 4;
+    for (int i0 = threadIdx.x; i0 < H; i0 += U * blockDim.x) {
+        float a[U], b[U], c[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * blockDim.x;
+            a[u] = i < H ? x[base + i] : 0.f;
+            b[u] = (x0 != nullptr && i < H) ? x0[base + i] : 0.f;
+            c[u] = i < H ? vec[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < H) x[base + i] = (x0 != nullptr ? a[u] + b[u] : a[u]) + c[u];
+        }
     }
 }
 
@@ -382,14 +458,18 @@ void head_norm_rope_write(const float* qkv, int ld, const int32_t* positions, co
     DLM_CHECK(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= d, "head_norm_rope_write: rotated dims must be even and <= d");
     DLM_CHECK(rot_dims == 0 || inv_freq != nullptr, "head_norm_rope_write: a rotation needs its table");
     int* err = error_flag_ptr();
-    const int warps = 4;
-    const dim3 grid(T, (nh + 2 * nkv + warps - 1) / warps);
+    const int warps = 8;
+    int gy = (nh + 2 * nkv + warps - 1) / warps;            // a head a warp while the blocks are few (a decode step);
+    while (gy > 1 && (long long)T * gy > 16 * 148) gy = (gy + 1) / 2;   // on a prompt several heads a warp: a block's
+    const dim3 grid(T, gy);                                  // opening (slot, sines) is most of a one-head warp's work
+    const size_t stage = ((size_t)warps * d + rot_dims) * sizeof(float);
+    DLM_CHECK(stage <= 48 * 1024, "head_norm_rope_write: head size too large");
     if (dtype == F32)
-        launch_dep(head_norm_rope_write_kernel<float>, grid, dim3(32 * warps), 0, stream, qkv, ld, positions, qn_w, kn_w, eps,
+        launch_dep(head_norm_rope_write_kernel<float>, grid, dim3(32 * warps), stage, stream, qkv, ld, positions, qn_w, kn_w, eps,
                    inv_freq, rot_dims, interleaved, slots, static_cast<float*>(q_out), static_cast<float*>(k_cache),
                    static_cast<float*>(v_cache), nh, nkv, d, dv, D, page_size, total_pages, err);
     else
-        launch_dep(head_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(32 * warps), 0, stream, qkv, ld, positions, qn_w,
+        launch_dep(head_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(32 * warps), stage, stream, qkv, ld, positions, qn_w,
                    kn_w, eps, inv_freq, rot_dims, interleaved, slots, static_cast<__nv_bfloat16*>(q_out),
                    static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), nh, nkv, d, dv, D,
                    page_size, total_pages, err);
@@ -409,12 +489,16 @@ void head_gate(void* o, const float* gate, int ldg, int T, int nh, int D, float 
 void norm_add_norm(float* resid, const float* y, const float* w_post, const float* w_next, float eps, void* out, int T,
                    int H, int out_dtype, cudaStream_t stream) {
     if (T <= 0) return;
+    const size_t rows = (size_t)2 * H * sizeof(float);
+    const int staged = rows <= 40 * 1024 ? 1 : 0;
+    const size_t smem = staged ? rows : 0;
+    const dim3 block(H > 2048 ? 512 : 256);
     if (out_dtype == F32)
-        launch_dep(norm_add_norm_kernel<float>, dim3(T), dim3(256), 0, stream, resid, y, w_post, w_next, eps,
-                   static_cast<float*>(out), H);
+        launch_dep(norm_add_norm_kernel<float>, dim3(T), block, smem, stream, resid, y, w_post, w_next, eps,
+                   static_cast<float*>(out), H, staged);
     else
-        launch_dep(norm_add_norm_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, resid, y, w_post, w_next, eps,
-                   static_cast<__nv_bfloat16*>(out), H);
+        launch_dep(norm_add_norm_kernel<__nv_bfloat16>, dim3(T), block, smem, stream, resid, y, w_post, w_next, eps,
+                   static_cast<__nv_bfloat16*>(out), H, staged);
     check_launch("norm_add_norm");
 }
 

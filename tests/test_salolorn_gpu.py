@@ -239,6 +239,20 @@ def test_gate_per_head_norm_add_norm_and_pass_entry(ops, dtype):
     ref.head_gate(want, gate.cpu(), nh, D, 1.3)
     ops.head_gate(o, gate, nh, D, 1.3)
     assert torch.allclose(o.float().cpu(), want.float(), atol=1e-5 if dtype == torch.float32 else 3e-2, rtol=1e-2)
+    # rows that stay in shared memory, rows that take a larger block, and rows too long to stay there
+    for W in (200, 2304, 5400):
+        _norm_add_norm_case(ops, ref, T, W, dtype)
+    W = 200
+    x, x0, vec = randn(T, W, seed=7), randn(T, W, seed=8), randn(W, seed=9)
+    a = x.clone()
+    ops.add_vec_rows(a, None, vec)
+    assert torch.equal(a, x + vec)
+    ops.add_vec_rows(a, x0, vec)
+    assert torch.allclose(a, x + vec + x0 + vec, atol=1e-6)
+    ops.check_errors()
+
+
+def _norm_add_norm_case(ops, ref, T, W, dtype):
     resid, y = randn(T, W, seed=3), randn(T, W, seed=4, std=5.0)
     w1, w2 = randn(W, seed=5, std=0.2) + 1.0, randn(W, seed=6, std=0.2) + 0.7
     for nxt in (w2, None):
@@ -251,13 +265,6 @@ def test_gate_per_head_norm_add_norm_and_pass_entry(ops, dtype):
         if nxt is not None:
             assert n_got.dtype == dtype
             assert torch.allclose(n_got.float().cpu(), n_want.float(), atol=1e-5 if dtype == torch.float32 else 2e-2, rtol=1e-2)
-    x, x0, vec = randn(T, W, seed=7), randn(T, W, seed=8), randn(W, seed=9)
-    a = x.clone()
-    ops.add_vec_rows(a, None, vec)
-    assert torch.equal(a, x + vec)
-    ops.add_vec_rows(a, x0, vec)
-    assert torch.allclose(a, x + vec + x0 + vec, atol=1e-6)
-    ops.check_errors()
 
 
 # ------------------------------------------------------------------ attention inside chunks, with a sink
