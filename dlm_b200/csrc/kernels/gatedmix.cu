@@ -26,7 +26,8 @@ __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.w
 // A block owns (head, request, a run of value columns).  Column j of S is shared by PARTS neighbouring lanes; a
 // lane keeps NG groups of four neighbouring rows in registers (group ig * PARTS + part), so that q, k and the decays
 // of its rows come from shared memory as 128-bit loads.  Rows beyond dk (up to 4 NG PARTS) are zeros with a decay
-// of one and change nothing.  S^T k and S^T q are added per lane and meet in a butterfly of shuffles, so the order
+// of one and change nothing.  S^T k and S^T q are added per lane and meet in a butterfly of shuffles (one for both
+// with the delta rule, whose read-out is taken from the decayed state and completed by u (k . q)), so the order
 // of every sum is fixed by dk alone and a request's result does not depend on how its tokens were cut into steps.
 // Tokens are staged in tiles in two buffers: while every thread walks one tile's tokens in order, asynchronous
 // copies bring the next tile's raw values; a warp per token then takes the lengths of q and k when they are to be
@@ -41,7 +42,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                                   float q_scale, int decay_kind, float inv_tau, int tile) {
     dep_wait();
     constexpr int DKP = 4 * NG * PARTS;                   // rows as the block keeps them
-    extern __shared__ __align__(16) float sm[];           // 2 x [tile][q: DKP | k: DKP | a: DKP (a decay per channel) | v | a0, beta]
+    extern __shared__ __align__(16) float sm[];           // 2 x [tile][q: DKP | k: DKP | a: DKP (a decay per channel) | v | a0, beta, k . q, -]
     const int h = blockIdx.x, r = blockIdx.y;
     const int cols = blockDim.x / PARTS;
     const int colsp = (cols + 3) & ~3;
@@ -110,7 +111,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
         for (int tok = warp; tok < n; tok += nwarp) {      // lengths, decays and write strengths of the tile
             float* row = cur + (size_t)tok * rl;
             float qv[DKP / 32 > 0 ? DKP / 32 : 1], kv[DKP / 32 > 0 ? DKP / 32 : 1];
-            float sq = 0.f, sk = 0.f;
+            float sq = 0.f, sk = 0.f, skq = 0.f;
 #pragma unroll
             for (int ii = 0; ii * 32 < DKP; ++ii) {
                 const int i = lane + 32 * ii;
@@ -118,6 +119,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                 kv[ii] = i < DKP ? row[DKP + i] : 0.f;
                 sq = fmaf(qv[ii], qv[ii], sq);
                 sk = fmaf(kv[ii], kv[ii], sk);
+                skq = fmaf(qv[ii], kv[ii], skq);
             }
             if (decay_kind == 0) {
                 if (lane == 0) row[off_s] = expf(neg_rate * softplus_g(row[off_s] + bias0));
@@ -133,6 +135,10 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                 sk = warp_sum(sk);
                 fq = q_scale * (1.0f / sqrtf(sq + unit_eps));
                 fk = 1.0f / sqrtf(sk + unit_eps);
+            }
+            if (DELTA) {
+                skq = warp_sum(skq);
+                if (lane == 2) row[off_s + 2] = skq * (fq * fk);
             }
 #pragma unroll
             for (int ii = 0; ii * 32 < DKP; ++ii) {
@@ -152,49 +158,72 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
             const float4* q4 = reinterpret_cast<const float4*>(row);
             const float4* k4 = reinterpret_cast<const float4*>(row + DKP);
             const float4* a4 = reinterpret_cast<const float4*>(row + 2 * DKP);
-            const float2 sc = *reinterpret_cast<const float2*>(row + off_s);      // decay of the head, write strength
+            const float4 sc = *reinterpret_cast<const float4*>(row + off_s);      // decay of the head, write strength, k . q
             float4 kk[NG];
-            float ksum = 0.f;
-#pragma unroll
-            for (int ig = 0; ig < NG; ++ig) {
-                const int g = ig * PARTS + part;
-                kk[ig] = k4[g];
-                if (decay_kind == 0) {
-                    s[4 * ig] *= sc.x; s[4 * ig + 1] *= sc.x; s[4 * ig + 2] *= sc.x; s[4 * ig + 3] *= sc.x;
-                } else {
-                    const float4 a = a4[g];
-                    s[4 * ig] *= a.x; s[4 * ig + 1] *= a.y; s[4 * ig + 2] *= a.z; s[4 * ig + 3] *= a.w;
-                }
-                if (DELTA) {
-                    float p = kk[ig].x * s[4 * ig];
-                    p = fmaf(kk[ig].y, s[4 * ig + 1], p);
-                    p = fmaf(kk[ig].z, s[4 * ig + 2], p);
-                    p = fmaf(kk[ig].w, s[4 * ig + 3], p);
-                    ksum += p;
-                }
-            }
-            float u = live ? row[off_v + col] : 0.f;
+            float acc;
             if (DELTA) {
+                // Both read-outs are taken from the decayed state, so that they meet in one butterfly:
+                // S'^T q = (aS)^T q + u (k . q) with S' = aS + k u^T; k . q comes with the tile.
+                float ksum = 0.f, qsum = 0.f;
 #pragma unroll
-                for (int x = PARTS >> 1; x > 0; x >>= 1) ksum += __shfl_xor_sync(0xffffffffu, ksum, x);
-                u = sc.y * (u - ksum);
+                for (int ig = 0; ig < NG; ++ig) {
+                    const int g = ig * PARTS + part;
+                    kk[ig] = k4[g];
+                    const float4 qq = q4[g];
+                    if (decay_kind == 0) {
+                        s[4 * ig] *= sc.x; s[4 * ig + 1] *= sc.x; s[4 * ig + 2] *= sc.x; s[4 * ig + 3] *= sc.x;
+                    } else {
+                        const float4 a = a4[g];
+                        s[4 * ig] *= a.x; s[4 * ig + 1] *= a.y; s[4 * ig + 2] *= a.z; s[4 * ig + 3] *= a.w;
+                    }
+                    float p = kk[ig].x * s[4 * ig], r = qq.x * s[4 * ig];
+                    p = fmaf(kk[ig].y, s[4 * ig + 1], p); r = fmaf(qq.y, s[4 * ig + 1], r);
+                    p = fmaf(kk[ig].z, s[4 * ig + 2], p); r = fmaf(qq.z, s[4 * ig + 2], r);
+                    p = fmaf(kk[ig].w, s[4 * ig + 3], p); r = fmaf(qq.w, s[4 * ig + 3], r);
+                    ksum += p;
+                    qsum += r;
+                }
+#pragma unroll
+                for (int x = PARTS >> 1; x > 0; x >>= 1) {
+                    ksum += __shfl_xor_sync(0xffffffffu, ksum, x);
+                    qsum += __shfl_xor_sync(0xffffffffu, qsum, x);
+                }
+                const float u = sc.y * ((live ? row[off_v + col] : 0.f) - ksum);
+                acc = fmaf(u, sc.z, qsum);
+#pragma unroll
+                for (int ig = 0; ig < NG; ++ig) {
+                    s[4 * ig] = fmaf(kk[ig].x, u, s[4 * ig]);
+                    s[4 * ig + 1] = fmaf(kk[ig].y, u, s[4 * ig + 1]);
+                    s[4 * ig + 2] = fmaf(kk[ig].z, u, s[4 * ig + 2]);
+                    s[4 * ig + 3] = fmaf(kk[ig].w, u, s[4 * ig + 3]);
+                }
+            } else {
+                const float u = live ? row[off_v + col] : 0.f;
+                acc = 0.f;
+#pragma unroll
+                for (int ig = 0; ig < NG; ++ig) {
+                    const int g = ig * PARTS + part;
+                    kk[ig] = k4[g];
+                    const float4 qq = q4[g];
+                    if (decay_kind == 0) {
+                        s[4 * ig] *= sc.x; s[4 * ig + 1] *= sc.x; s[4 * ig + 2] *= sc.x; s[4 * ig + 3] *= sc.x;
+                    } else {
+                        const float4 a = a4[g];
+                        s[4 * ig] *= a.x; s[4 * ig + 1] *= a.y; s[4 * ig + 2] *= a.z; s[4 * ig + 3] *= a.w;
+                    }
+                    s[4 * ig] = fmaf(kk[ig].x, u, s[4 * ig]);
+                    s[4 * ig + 1] = fmaf(kk[ig].y, u, s[4 * ig + 1]);
+                    s[4 * ig + 2] = fmaf(kk[ig].z, u, s[4 * ig + 2]);
+                    s[4 * ig + 3] = fmaf(kk[ig].w, u, s[4 * ig + 3]);
+                    float p = qq.x * s[4 * ig];
+                    p = fmaf(qq.y, s[4 * ig + 1], p);
+                    p = fmaf(qq.z, s[4 * ig + 2], p);
+                    p = fmaf(qq.w, s[4 * ig + 3], p);
+                    acc += p;
+                }
+#pragma unroll
+                for (int x = PARTS >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
             }
-            float acc = 0.f;
-#pragma unroll
-            for (int ig = 0; ig < NG; ++ig) {
-                const float4 qq = q4[ig * PARTS + part];
-                s[4 * ig] = fmaf(kk[ig].x, u, s[4 * ig]);
-                s[4 * ig + 1] = fmaf(kk[ig].y, u, s[4 * ig + 1]);
-                s[4 * ig + 2] = fmaf(kk[ig].z, u, s[4 * ig + 2]);
-                s[4 * ig + 3] = fmaf(kk[ig].w, u, s[4 * ig + 3]);
-                float p = qq.x * s[4 * ig];
-                p = fmaf(qq.y, s[4 * ig + 1], p);
-                p = fmaf(qq.z, s[4 * ig + 2], p);
-                p = fmaf(qq.w, s[4 * ig + 3], p);
-                acc += p;
-            }
-#pragma unroll
-            for (int x = PARTS >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
             if (live && part == 0) o[(long long)(first + tok) * ldo + h * dv + j] = acc;
         }
     }
