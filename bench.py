@@ -1261,7 +1261,8 @@ def main() -> int:
     m.eng.rt.ops.check_errors()
     m.close()
     if not args.no_extras and not args.no_points:
-        sv_args = argparse.Namespace(layers=MODEL_A["num_hidden_layers"])
+        sv_args = argparse.Namespace(layers=MODEL_A["num_hidden_layers"], serving_prompts=args.serving_prompts,
+                                     serving_requests=args.serving_requests)
         sv = run_serving(sv_args)
         out["serving"] = {"generated_tok_s": sv["value"], "prompt_tok_s": sv["prompt_tok_s"], "seconds": sv["seconds"],
                           "steps": sv["steps"], "mean_step_ms": round(1e3 * sv["seconds"] / max(sv["steps"], 1), 3),
