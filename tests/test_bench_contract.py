@@ -47,3 +47,16 @@ def test_roofline_bytes_of_a_hand_made_case():
     # at least every matrix that one token uses, once; nothing the size of the whole expert table
     assert got >= 2 * (qkv + o + routed + shared + head)
     assert got < 2 * (qkv + o + 4 * 3 * 8 * 6 + shared + head) + 4096
+
+
+def test_the_default_lines_serving_extra_gets_every_argument_it_reads():
+    """The default line runs the serving workload with an argument set of its own making: every `args.<name>` that
+    `run_serving` reads has to be in it."""
+    import inspect
+    import re
+    sys.path.insert(0, ROOT)
+    import bench
+    read = set(re.findall(r"\bargs\.([a-z_0-9]+)", inspect.getsource(bench.run_serving)))
+    made = re.search(r"sv_args = argparse\.Namespace\((.*?)\)\n", inspect.getsource(bench.main), re.S).group(1)
+    given = set(re.findall(r"\b([a-z_0-9]+)=", made))
+    assert read and read <= given, read - given
