@@ -580,3 +580,28 @@ def test_command_line_with_random_weights(tmp_path):
             if float(top2[0] - top2[1]) > 1e-3 * spread:
                 assert int(torch.argmax(row)) == tok
             seq.append(tok)
+
+
+MID = {"architecture": "Salolorn", "vocab": 1000, "width": 320, "norm": {"eps": 1e-6}, "logit_scale": 0.8,
+       "loop": {"start": 1, "stop": 3, "times": 2},
+       "layers": [latent(5, 48, 16, 40, 96, 0.12, 1e4, dense(448)), delta(6, 3, 48, 80, 4, dense(512)),
+                  parallel(left(10, 5, 80, 48, 0.11, 100, 1e4, 40), right(5, 24, 72, 6.0), 0.9, 1.1, dense(384)),
+                  delta(4, 4, 96, 32, 2)]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wider_model_with_a_long_request(dtype, tmp_path):
+    """Sizes between the tiny configurations and a real model's (products large enough for the tensor-core kernels,
+    head sizes that are no power of two, chunks of 100 positions over pages of 64), a request of 700 tokens beside
+    short ones: whole, decoded, in portions and mixed."""
+    tensors = write_model(MID, str(tmp_path / "m"), seed=5)
+    oracle = plain.PlainSalolorn(MID, tensors)
+    reqs = {f"r{i}": tokens(i, n, MID["vocab"]) for i, n in enumerate([37, 130, 700])}
+    ref, lim = references(oracle, reqs, dtype)
+    eng = gpu_engine(str(tmp_path / "m"), dtype, page_size=64, num_pages=32)
+    mixed, _ = cuttings.mixed(reqs, max_live=3, seed=2, decode_tail=40)
+    for what, steps in (("whole", cuttings.whole(reqs)), ("decode", cuttings.tail_decode(reqs, 110)),
+                        ("portions", cuttings.portions(reqs)), ("mixed", mixed)):
+        got = cuttings.run_trace(eng, steps)
+        eng.rt.ops.check_errors()
+        assert worst_ratio(got, ref, lim) < 1.0, (what, worst_ratio(got, ref, lim))
