@@ -58,14 +58,15 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
 // A score is dot * scale - slopes[query head] * (query position - key position); slopes (f32 [nh], made at load,
 // never written by a kernel) == nullptr: no distance term.  chunk > 0: a query at p sees only keys from
 // floor(p / chunk) * chunk on (chunks are counted from a request's position 0).  sinks (f32 [nh]) != nullptr: the
-// softmax's denominator also holds exp(sinks[head]), unscaled, without key or value.
+// softmax's denominator also holds exp(sinks[head]), unscaled, without key or value.  softcap c > 0: the scaled dot
+// product becomes c * tanh(dot * scale / c) before the distance term and the mask.
 // num_single: how many requests have exactly one query token.  With fast != 0 and a scratch buffer of
 // attention_scratch_floats(...) floats those go to the split-key decode kernel.
 void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
                const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
                int page_size, int total_pages, int window, float scale, const float* slopes, int chunk,
-               const float* sinks, int max_q_len, int max_kv_len, int num_single, float* scratch, int dtype, int fast,
-               cudaStream_t stream);
+               const float* sinks, float softcap, int max_q_len, int max_kv_len, int num_single, float* scratch, int dtype,
+               int fast, cudaStream_t stream);
 // Floats of scratch the decode kernel needs for a step of R requests whose longest holds max_kv_len tokens.
 size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 
@@ -73,7 +74,8 @@ size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 // score_fn 2: softmax as for 0, but select_bias[E] is the router's own bias and is added to the logits first
 // (it then enters scores and choice alike; with norm != 0 the weights are the softmax over the chosen logits);
 // the k best scores (ties: lower index; with select_bias[E] the choice is made on score + bias and the weight
-// stays the score); norm != 0: the chosen weights are divided by their sum; all are multiplied by `scale`.
+// stays the score); norm != 0: the chosen weights are divided by their sum (norm 2: by their sum + 1e-20); all are
+// multiplied by `scale`.
 // has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).  The input h is: activations of the weights' dtype
 // (default); the 32-bit residual, with rmsnorm(h, norm_w, eps) applied first in 32-bit (norm_w != nullptr); or
 // 32-bit activations that are already normalised (h_is_f32 != 0).  dtype is the weights' dtype.
@@ -98,9 +100,12 @@ int router_topk_permute(const void* h, const void* w, const float* norm_w, float
 void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int32_t* rows, int32_t* dest,
                  cudaStream_t stream);
 
-// resid[t, :] += sum_j wts[t, j] * y[dest[t, j], :] (+ gate[t] * shared[t, :]); gate == nullptr: 1.
+// resid[t, :] += sum_j wts[t, j] * y[dest[t, j], :] (+ shared_scale * gate[t] * shared[t, :]); gate == nullptr: 1.
+// ids (i32 [T, k]) != nullptr: a pair whose expert id is num_real or more reads passthrough[t, :] (f32 [T, H]) in
+// place of its row of y (an expert that hands its input through; y may then be nullptr when num_real is 0).
 void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
-                 float* resid, int T, int H, int k, cudaStream_t stream);
+                 float* resid, int T, int H, int k, const int32_t* ids, int num_real, const float* passthrough,
+                 float shared_scale, cudaStream_t stream);
 
 // out[i] = index of the first maximum of logits[i, :].  scratch: argmax_scratch_bytes(N, V) bytes (may be
 // nullptr when that is 0; a large vocabulary is then searched by one block per row).
@@ -167,9 +172,11 @@ void table_lookup(const int32_t* tokens, const int32_t* table, int32_t* ids, flo
 
 // Norm over groups of `group_size` channels with a gate.  mode 0: v = y * silu(gate), out = v / rms(v) * w;
 // mode 1: out = y / rms(y) * w * sigmoid(gate); mode 2: out = y / rms(y) * w * silu(gate).  y, gate f32 (row strides
-// ldy, ldg), w f32 [groups * group_size] or nullptr (every weight 1).
+// ldy, ldg), w f32 [groups * group_size] or nullptr (every weight 1).  row_scale (f32 [T, groups], modes 1 and 2) !=
+// nullptr: y[t, group] is multiplied by row_scale[t, group] before anything else.
 void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const float* w, void* out, int ldo, int T,
-                   int groups, int group_size, float eps, int mode, int out_dtype, cudaStream_t stream);
+                   int groups, int group_size, float eps, int mode, int out_dtype, const float* row_scale,
+                   cudaStream_t stream);
 
 // State-space scan.  xbc f32 rows [x: heads * P | B: groups * N | C: groups * N]; dt_raw f32 [T, heads] (row stride
 // lddt); state f32 [slots, heads, N, P]; y f32 [T, heads * P].  Per head (group = head / (heads / groups)):
@@ -297,5 +304,33 @@ void norm_add_norm(float* resid, const float* y, const float* w_post, const floa
 
 // x[t, :] += (x0 != nullptr ? x0[t, :] : 0) + vec[:]   (all f32)
 void add_vec_rows(float* x, const float* x0, const float* vec, int T, int H, cudaStream_t stream);
+
+// The recurrence of gated_scan with exponential gates kept in range by a running maximum, and a normaliser:
+//   i = cap tanh((igate[t, h] + i_bias[h]) / cap);   f = log sigmoid(cap tanh((fgate[t, h] + f_bias[h]) / cap));
+//   m' = max(f + m, i);   S <- exp(f + m - m') S + exp(i - m') k v^T;   n <- exp(f + m - m') n + exp(i - m') k;
+//   o = S^T q (q times q_scale);   rden[t, h] = 1 / (max(|n . q|, exp(-m')) + den_eps).
+// q, k f32 rows of heads * dk, v of heads * dv (row strides given), igate and fgate f32 [T, heads] raw.  state f32
+// [slots, heads, dk, dv], nstate [slots, heads, dk], mstate [slots, heads, dv + 1] (equal copies of m, one per column
+// of a block; all zero at a request's start).  o f32 rows of heads * dv (not yet divided), rden f32 [T, heads].
+void memory_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* igate, int ldi,
+                 const float* fgate, int ldf, const float* i_bias, const float* f_bias, float cap, float* state,
+                 float* nstate, float* mstate, const int32_t* cu_q, const int32_t* state_slot, float* o, int ldo,
+                 float* rden, int R, int heads, int dk, int dv, float q_scale, float den_eps, cudaStream_t stream);
+
+// ---- layers that squash instead of norming (capmix.cu) ----
+
+// out[i, :] = tanh(alpha * x[rows ? rows[i] : i, :]) * w + b   (x, w, b f32; out in out_dtype)
+void dyt_norm(const float* x, const int32_t* rows, const float* w, const float* b, float alpha, void* out, int n_rows,
+              int H, int out_dtype, cudaStream_t stream);
+// The same rows through two such norms in one pass: out_a with (wa, ba, alpha_a), out_b with (wb, bb, alpha_b), and,
+// with out_b32 != nullptr, the second result once more in 32-bit.
+void dyt_norm_pair(const float* x, const float* wa, const float* ba, float alpha_a, void* out_a, const float* wb,
+                   const float* bb, float alpha_b, void* out_b, float* out_b32, int T, int H, int out_dtype,
+                   cudaStream_t stream);
+// x[i] = cap * tanh(x[i] / cap) for n floats, in place
+void tanh_cap(float* x, long long n, float cap, cudaStream_t stream);
+// o[t, h * D + i] *= factor * sigmoid(gate[t * ldg + h * dv + i]) for i < dv, in place (o in `dtype`, gate f32 raw)
+void entry_gate(void* o, const float* gate, int ldg, int T, int nh, int dv, int D, float factor, int dtype,
+                cudaStream_t stream);
 
 }  // namespace dlmk

@@ -15,9 +15,10 @@ size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len) 
 void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
                const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
                int page_size, int total_pages, int window, float scale, const float* slopes, int chunk,
-               const float* sinks, int max_q_len, int max_kv_len, int num_single, float* scratch, int dtype, int fast,
-               cudaStream_t stream) {
-    const Score score(scale, slopes, chunk, sinks);
+               const float* sinks, float softcap, int max_q_len, int max_kv_len, int num_single, float* scratch, int dtype,
+               int fast, cudaStream_t stream) {
+    const Score score(scale, slopes, chunk, sinks, softcap);
+    DLM_CHECK(softcap >= 0.f, "attention: a score cap is positive (0: none)");
     if (T <= 0 || R <= 0) return;
     DLM_CHECK(chunk >= 0, "attention: a chunk size is positive (0: none)");
     const bool decode = fast && num_single > 0 && scratch != nullptr && attention_decode_ok(hd) &&

@@ -175,7 +175,9 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kf[u][i], d);
 #pragma unroll
                         for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                        s[u] = ok[u] ? d * scale.scale - slope[g] * (float)(p - (j0 + kb + ks + u * STREAMS)) : -INFINITY;
+                        const float far = slope[g] * (float)(p - (j0 + kb + ks + u * STREAMS));
+                        if (scale.softcap > 0.f) s[u] = ok[u] ? scale.softcap * tanhf((d * scale.scale) / scale.softcap) - far : -INFINITY;
+                        else s[u] = ok[u] ? d * scale.scale - far : -INFINITY;
                         mx = fmaxf(mx, s[u]);
                     }
                     if (mx != -INFINITY) {

@@ -130,8 +130,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
                             int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                             float* part_o, float* part_ml, int nh, int nkv, int page_size,
                             int page_shift, int total_pages, int window, float scale_log2, const float* __restrict__ slopes,
-                            int mask_chunk, const float* __restrict__ sinks, int chunk, int n_splits, int head_passes,
-                            __nv_bfloat16* out, int fuse_merge, int* err) {
+                            int mask_chunk, const float* __restrict__ sinks, float cap_in, float cap_out, int chunk,
+                            int n_splits, int head_passes, __nv_bfloat16* out, int fuse_merge, int* err) {
     constexpr int PITCH = HD + 8;
     constexpr int KS = HD / 16, DT = HD / 8, CPR = HD / 8;
     dep_wait();
@@ -256,8 +256,10 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int j = jw + n * 8 + 2 * t + (c & 1);
+                        // with a cap the score is cap * tanh(dot * scale / cap), in base-2 units
+                        const float far = (c < 2 ? slope_a : slope_b) * (float)(p - j);
                         const float v = (j >= j_begin && j < j_end)
-                            ? s[n][c] * scale_log2 - (c < 2 ? slope_a : slope_b) * (float)(p - j) : -INFINITY;
+                            ? (cap_out != 0.f ? cap_out * tanh_sfu(s[n][c] * cap_in) - far : s[n][c] * scale_log2 - far) : -INFINITY;
                         s[n][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -321,6 +323,7 @@ struct DecodeTmaParams {
     const float* slopes;
     int mask_chunk;
     const float* sinks;
+    float cap_in, cap_out;      // cap_out != 0: a score is cap_out * tanh(dot * cap_in) (base-2 units)
     int n_splits, head_passes;
     __nv_bfloat16* out; int fuse_merge;
     int* err;
@@ -460,8 +463,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int j = jw + n * 8 + 2 * t + (c & 1);
+                        const float far = (c < 2 ? slope_a : slope_b) * (float)(pos - j);
                         const float v = (j >= j_begin && j < j_end)
-                            ? sc[n][c] * p.scale_log2 - (c < 2 ? slope_a : slope_b) * (float)(pos - j) : -INFINITY;
+                            ? (p.cap_out != 0.f ? p.cap_out * tanh_sfu(sc[n][c] * p.cap_in) - far : sc[n][c] * p.scale_log2 - far) : -INFINITY;
                         sc[n][c] = v;
                         if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
                     }
@@ -555,7 +559,8 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
     launch_dep(kern, grid, WARPS * 32, smem, stream,
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv,
-        page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk, scale.sinks, chunk, n_splits,
+        page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk, scale.sinks,
+        scale.cap_in(), scale.cap_out(), chunk, n_splits,
         head_passes, static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr());
 }
 
@@ -592,7 +597,7 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
         const dim3 tma_grid(R, nkv * head_passes, splits);
         DecodeTmaParams p{static_cast<const __nv_bfloat16*>(q), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh,
                           nkv, page_size, shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk,
-                          scale.sinks, splits, head_passes,
+                          scale.sinks, scale.cap_in(), scale.cap_out(), splits, head_passes,
                           static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr()};
         // Blocks that have a multiprocessor to themselves keep six tiles in flight instead of three (8 requests
         // of 8,192 tokens: 4.72 -> 4.57 ms a step; of 1,030: 3.245 -> 3.235).

@@ -12,15 +12,31 @@ namespace dlmk {
 // chunk > 0: a query at p sees only keys j >= floor(p / chunk) * chunk (chunks are counted from position 0 of the
 // request).  sinks (f32 [nh], made at load) != nullptr: the softmax's denominator also holds exp(sinks[head]), a
 // logit without key or value that is not scaled.
+// softcap c > 0: the scaled dot product is squashed, c * tanh(dot * scale / c), before the distance term and the
+// mask; 0: it is used as it is.
 struct Score {
     float scale;
     const float* slopes;
     int chunk;
     const float* sinks;
-    Score(float s, const float* b = nullptr, int c = 0, const float* k = nullptr)
-        : scale(s), slopes(b), chunk(c), sinks(k) {}
+    float softcap;
+    Score(float s, const float* b = nullptr, int c = 0, const float* k = nullptr, float cap = 0.f)
+        : scale(s), slopes(b), chunk(c), sinks(k), softcap(cap) {}
     bool plain_mask() const { return chunk <= 0 && sinks == nullptr; }
+    // what the tensor-core kernels get: a squashed score in base-2 units is cap_out() * tanh(dot * cap_in())
+    float cap_in() const { return softcap > 0.f ? scale / softcap : 0.f; }
+    float cap_out() const { return softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; }
 };
+
+#ifdef __CUDACC__
+// tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1) on the special-function unit: an absolute error of a few 1e-7 everywhere
+// (the scores it squashes are then multiplied by a cap of tens at most), +-1 beyond the range of 2^x.
+__device__ __forceinline__ float tanh_sfu(float x) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+#endif
 
 // Which of the faster kernels take a chunked mask or a sink: the warp-level prefill kernel and every decode kernel
 // do; the tcgen05 prefill kernel does not (its steps go to the warp-level kernel then).

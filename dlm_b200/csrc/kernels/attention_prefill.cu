@@ -34,8 +34,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
                          int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int R, int nh, int nkv, int page_size, int total_pages,
-                         int page_shift, int window, float scale_log2, const float* __restrict__ slopes, int mask_chunk,
-                         const float* __restrict__ sinks, int skip_single, int n_sm, int* err) {
+                         int page_shift, int window, float scale_log2_arg, const float* __restrict__ slopes, int mask_chunk,
+                         const float* __restrict__ sinks, float cap_in, float cap_out, int skip_single, int n_sm,
+                         int* err) {
     constexpr int PITCH = HD + 8;              // elements per shared-memory row (16 bytes of padding)
     constexpr int KS = HD / 16;                // k16 steps over the head dimension
     constexpr int DT = HD / 8;                 // n8 tiles of the output
@@ -186,6 +187,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     mma16816(s[2 * jn + 1], qf, kf[1], kf[3]);
                 }
             }
+            if (cap_out != 0.f) {
+                // squashed scores: cap * tanh(dot * scale / cap), already in base-2 units; the scale below is then 1
+#pragma unroll
+                for (int j = 0; j < BKV / 8; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[j][c] = cap_out * tanh_sfu(s[j][c] * cap_in);
+            }
+            const float scale_log2 = cap_out != 0.f ? 1.0f : scale_log2_arg;
             // scale (to base 2), mask where needed, running maximum
             float mx_a = m_a, mx_b = m_b;
             const bool all_visible = j0 + BKV - 1 <= w_lo && (window <= 0 || w_hi - j0 < window) && j0 >= wc_hi;
@@ -312,8 +321,8 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
         static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, shift, window,
-        scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk, scale.sinks, skip_single, sm_count(),
-        error_flag_ptr());
+        scale.scale * 1.4426950408889634f, scale.slopes, scale.chunk, scale.sinks, scale.cap_in(), scale.cap_out(),
+        skip_single, sm_count(), error_flag_ptr());
 }
 
 }  // namespace

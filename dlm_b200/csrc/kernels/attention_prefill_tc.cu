@@ -435,7 +435,7 @@ bool attention_prefill_tc_ok(const void* q, const void* k_cache, const void* v_c
                              int page_size, Score scale) {
     // (the row maximum is taken before the scores are scaled: the scale must be positive, and a distance term
     // has no place in that order of steps)
-    return scale.scale > 0.f && scale.slopes == nullptr && scale.plain_mask() && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
+    return scale.scale > 0.f && scale.slopes == nullptr && scale.softcap == 0.f && scale.plain_mask() && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
            ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
              reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
 }

@@ -118,7 +118,8 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
             const float* kr = Ks + lane * (hd + 1);
             float s = 0.f;
             for (int d = 0; d < hd; ++d) s = fmaf(qv[d], kr[d], s);
-            s = s * scale.scale - slope * (float)(p - j);
+            if (scale.softcap > 0.f) s = scale.softcap * tanhf((s * scale.scale) / scale.softcap) - slope * (float)(p - j);
+            else s = s * scale.scale - slope * (float)(p - j);
             const bool visible = (j <= p) && (window <= 0 || p - j < window) &&
                                  (scale.chunk <= 0 || j >= (p / scale.chunk) * scale.chunk);
             if (!visible) s = -INFINITY;

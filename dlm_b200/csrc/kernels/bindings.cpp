@@ -44,12 +44,12 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("attention", [](u64 q, u64 k_cache, u64 v_cache, u64 block_table, int table_width, u64 cu_q, u64 kv_len,
                           u64 out, int T, int R, int nh, int nkv, int hd, int page_size, int total_pages, int window,
-                          float scale, u64 slopes, int chunk, u64 sinks, int max_q_len, int max_kv_len, int num_single,
-                          u64 scratch, int dtype, int fast, u64 stream) {
+                          float scale, u64 slopes, int chunk, u64 sinks, float softcap, int max_q_len, int max_kv_len,
+                          int num_single, u64 scratch, int dtype, int fast, u64 stream) {
         dlmk::attention(ptr<const void>(q), ptr<const void>(k_cache), ptr<const void>(v_cache),
                         ptr<const int32_t>(block_table), table_width, ptr<const int32_t>(cu_q),
                         ptr<const int32_t>(kv_len), ptr<void>(out), T, R, nh, nkv, hd, page_size, total_pages, window,
-                        scale, ptr<const float>(slopes), chunk, ptr<const float>(sinks), max_q_len, max_kv_len,
+                        scale, ptr<const float>(slopes), chunk, ptr<const float>(sinks), softcap, max_q_len, max_kv_len,
                         num_single, ptr<float>(scratch), dtype, fast, st(stream));
     });
     m.def("attention_scratch_floats", [](int R, int nh, int nkv, int hd, int max_kv_len) {
@@ -76,10 +76,11 @@ PYBIND11_MODULE(_dlm_kernels, m) {
         dlmk::moe_permute(ptr<const int32_t>(ids), n, k, E, ptr<int32_t>(offsets), ptr<int32_t>(rows),
                           ptr<int32_t>(dest), st(stream));
     });
-    m.def("moe_combine", [](u64 y, u64 dest, u64 wts, u64 shared, u64 gate, u64 resid, int T, int H, int k,
-                            u64 stream) {
+    m.def("moe_combine", [](u64 y, u64 dest, u64 wts, u64 shared, u64 gate, u64 resid, int T, int H, int k, u64 ids,
+                            int num_real, u64 passthrough, float shared_scale, u64 stream) {
         dlmk::moe_combine(ptr<const float>(y), ptr<const int32_t>(dest), ptr<const float>(wts),
-                          ptr<const float>(shared), ptr<const float>(gate), ptr<float>(resid), T, H, k, st(stream));
+                          ptr<const float>(shared), ptr<const float>(gate), ptr<float>(resid), T, H, k,
+                          ptr<const int32_t>(ids), num_real, ptr<const float>(passthrough), shared_scale, st(stream));
     });
     m.def("argmax", [](u64 logits, u64 out, int N, int V, u64 scratch, u64 stream) {
         dlmk::argmax(ptr<const float>(logits), ptr<int32_t>(out), N, V, ptr<void>(scratch), st(stream));
@@ -131,9 +132,9 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                            V, top, E, st(stream));
     });
     m.def("gated_rmsnorm", [](u64 y, int ldy, u64 gate, int ldg, u64 w, u64 out, int ldo, int T, int groups,
-                              int group_size, float eps, int mode, int out_dtype, u64 stream) {
+                              int group_size, float eps, int mode, int out_dtype, u64 row_scale, u64 stream) {
         dlmk::gated_rmsnorm(ptr<const float>(y), ldy, ptr<const float>(gate), ldg, ptr<const float>(w), ptr<void>(out),
-                            ldo, T, groups, group_size, eps, mode, out_dtype, st(stream));
+                            ldo, T, groups, group_size, eps, mode, out_dtype, ptr<const float>(row_scale), st(stream));
     });
     m.def("ssm_scan", [](u64 xbc, int ldx, u64 dt_raw, int lddt, u64 dt_bias, u64 A_log, u64 D, u64 state, u64 cu_q,
                          u64 state_slot, u64 y, int R, int heads, int P, int N, int groups, u64 fixed_decay,
@@ -240,6 +241,31 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("add_vec_rows", [](u64 x, u64 x0, u64 vec, int T, int H, u64 stream) {
         dlmk::add_vec_rows(ptr<float>(x), ptr<const float>(x0), ptr<const float>(vec), T, H, st(stream));
+    });
+    m.def("memory_scan", [](u64 q, int ldq, u64 k, int ldk, u64 v, int ldv, u64 igate, int ldi, u64 fgate, int ldf,
+                            u64 i_bias, u64 f_bias, float cap, u64 state, u64 nstate, u64 mstate, u64 cu_q, u64 state_slot,
+                            u64 o, int ldo, u64 rden, int R, int heads, int dk, int dv, float q_scale, float den_eps,
+                            u64 stream) {
+        dlmk::memory_scan(ptr<const float>(q), ldq, ptr<const float>(k), ldk, ptr<const float>(v), ldv,
+                          ptr<const float>(igate), ldi, ptr<const float>(fgate), ldf, ptr<const float>(i_bias),
+                          ptr<const float>(f_bias), cap, ptr<float>(state), ptr<float>(nstate), ptr<float>(mstate),
+                          ptr<const int32_t>(cu_q), ptr<const int32_t>(state_slot), ptr<float>(o), ldo, ptr<float>(rden),
+                          R, heads, dk, dv, q_scale, den_eps, st(stream));
+    });
+    m.def("dyt_norm", [](u64 x, u64 rows, u64 w, u64 b, float alpha, u64 out, int n_rows, int H, int out_dtype,
+                         u64 stream) {
+        dlmk::dyt_norm(ptr<const float>(x), ptr<const int32_t>(rows), ptr<const float>(w), ptr<const float>(b), alpha,
+                       ptr<void>(out), n_rows, H, out_dtype, st(stream));
+    });
+    m.def("dyt_norm_pair", [](u64 x, u64 wa, u64 ba, float alpha_a, u64 out_a, u64 wb, u64 bb, float alpha_b, u64 out_b,
+                              u64 out_b32, int T, int H, int out_dtype, u64 stream) {
+        dlmk::dyt_norm_pair(ptr<const float>(x), ptr<const float>(wa), ptr<const float>(ba), alpha_a, ptr<void>(out_a),
+                            ptr<const float>(wb), ptr<const float>(bb), alpha_b, ptr<void>(out_b), ptr<float>(out_b32),
+                            T, H, out_dtype, st(stream));
+    });
+    m.def("tanh_cap", [](u64 x, long long n, float cap, u64 stream) { dlmk::tanh_cap(ptr<float>(x), n, cap, st(stream)); });
+    m.def("entry_gate", [](u64 o, u64 gate, int ldg, int T, int nh, int dv, int D, float factor, int dtype, u64 stream) {
+        dlmk::entry_gate(ptr<void>(o), ptr<const float>(gate), ldg, T, nh, dv, D, factor, dtype, st(stream));
     });
     m.def("take_error_flag", &dlmk::take_error_flag);
     m.def("reset_decode_merge_counters", [](u64 stream) { dlmk::reset_decode_merge_counters(st(stream)); });

@@ -345,19 +345,25 @@ __global__ void gather_rows_kernel(const uint4* src, const int32_t* rows,
 template <bool VEC>
 __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
                                    const float* wts, const float* shared,
-                                   const float* gate, float* resid, int H, int k) {
+                                   const float* gate, float* resid, int H, int k, const int32_t* ids, int num_real,
+                                   const float* passthrough, float shared_scale) {
     dep_wait();
     dep_launch_next();
     const int t = blockIdx.x;
     float* r = resid + (long long)t * H;
+    // where pair (t, j) reads: its row of y, or the token's own row when its expert hands the input through
+    auto source = [&](int j) -> const float* {
+        if (ids != nullptr && ids[t * k + j] >= num_real) return passthrough + (long long)t * H;
+        return y + (long long)dest[t * k + j] * H;
+    };
     if constexpr (VEC) {
         // four columns a thread; per element the same sums in the same order as below
-        const float g = (shared != nullptr && gate != nullptr) ? gate[t] : 1.0f;
+        const float g = ((shared != nullptr && gate != nullptr) ? gate[t] : 1.0f) * shared_scale;
         for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H / 4; i += blockDim.x * gridDim.y) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int j = 0; j < k; ++j) {
                 const float wj = wts[t * k + j];
-                const float4 v = *reinterpret_cast<const float4*>(y + (long long)dest[t * k + j] * H + 4 * i);
+                const float4 v = *reinterpret_cast<const float4*>(source(j) + 4 * i);
                 acc.x = fmaf(wj, v.x, acc.x); acc.y = fmaf(wj, v.y, acc.y);
                 acc.z = fmaf(wj, v.z, acc.z); acc.w = fmaf(wj, v.w, acc.w);
             }
@@ -374,9 +380,9 @@ __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
         for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += blockDim.x * gridDim.y) {
             float acc = 0.f;
             for (int j = 0; j < k; ++j)
-                acc = fmaf(wts[t * k + j], y[(long long)dest[t * k + j] * H + i], acc);
+                acc = fmaf(wts[t * k + j], source(j)[i], acc);
             if (shared != nullptr) {
-                const float g = gate ? gate[t] : 1.0f;
+                const float g = (gate ? gate[t] : 1.0f) * shared_scale;
                 acc = fmaf(g, shared[(long long)t * H + i], acc);
             }
             r[i] += acc;
@@ -459,15 +465,18 @@ void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, in
 }
 
 void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
-                 float* resid, int T, int H, int k, cudaStream_t stream) {
+                 float* resid, int T, int H, int k, const int32_t* ids, int num_real, const float* passthrough,
+                 float shared_scale, cudaStream_t stream) {
     if (T <= 0) return;
+    DLM_CHECK(ids == nullptr || passthrough != nullptr, "moe_combine: experts that hand their input through need that input");
+    DLM_CHECK(y != nullptr || (ids != nullptr && num_real == 0), "moe_combine: the experts' outputs are missing");
     const bool vec = H % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(shared) |
-                                     reinterpret_cast<uintptr_t>(resid)) & 15) == 0;
+                                     reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(passthrough)) & 15) == 0;
     const int cols = vec ? H / 4 : H;
     int slices = (cols + 255) / 256;
     if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
-    if (vec) launch_dep(moe_combine_kernel<true>, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k);
-    else launch_dep(moe_combine_kernel<false>, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k);
+    if (vec) launch_dep(moe_combine_kernel<true>, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k, ids, num_real, passthrough, shared_scale);
+    else launch_dep(moe_combine_kernel<false>, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k, ids, num_real, passthrough, shared_scale);
     check_launch("moe_combine");
 }
 

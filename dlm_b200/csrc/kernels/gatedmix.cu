@@ -32,6 +32,25 @@ __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.w
 // Tokens are staged in tiles in two buffers: while every thread walks one tile's tokens in order, asynchronous
 // copies bring the next tile's raw values; a warp per token then takes the lengths of q and k when they are to be
 // unit vectors and turns the raw decay and write strength into factors.
+// What the recurrence with exponential gates and a running maximum (decay_kind 2) needs beside the common arguments.
+struct MaxGateArgs {
+    const float* igate; int ldi;        // raw input gate [T, heads] (the raw forget gate comes as `dec`)
+    const float* i_bias; const float* f_bias;   // [heads]
+    float cap, den_eps;
+    float* nstate;                      // [slots, heads, dk]: the normaliser n
+    float* mstate;                      // [slots, heads, dv + 1]: the running maximum, a copy per column
+    float* rden;                        // [T, heads]: 1 / (max(|n . q|, exp(-m)) + den_eps)
+};
+
+__device__ __forceinline__ float log_sigmoid_g(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// decay_kind 2 (never with DELTA): per head a log input gate i = cap tanh((raw_i + bias) / cap) and a log forget
+// gate f = log sigmoid(cap tanh((raw_f + bias) / cap)); with the running maximum m (carried in the state):
+// m' = max(f + m, i); S <- exp(f + m - m') S + exp(i - m') k v^T.  The normaliser n <- exp(f + m - m') n + exp(i - m') k
+// is kept as one more column of S (index dv, its "value" a constant one) by the block that owns that column; it
+// writes 1 / (max(|n . q|, exp(-m')) + den_eps) per token and head instead of an output.  The maxima of a tile are
+// taken by one thread in token order between two barriers; every block of a head does the same and keeps a copy of
+// m of its own (one per column it owns), so no block reads what another writes.
 template <int NG, int PARTS, bool DELTA>
 __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                                   const float* __restrict__ v, int ldv, const float* __restrict__ dec, int ldd,
@@ -39,7 +58,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                                   const float* __restrict__ dec_bias, float* state,
                                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ state_slot, float* o,
                                   int ldo, int heads, int qk_heads, int dk, int dv, int unit, float unit_eps,
-                                  float q_scale, int decay_kind, float inv_tau, int tile) {
+                                  float q_scale, int decay_kind, float inv_tau, int tile, MaxGateArgs mg) {
     dep_wait();
     constexpr int DKP = 4 * NG * PARTS;                   // rows as the block keeps them
     extern __shared__ __align__(16) float sm[];           // 2 x [tile][q: DKP | k: DKP | a: DKP (a decay per channel) | v | a0, beta, k . q, -]
@@ -49,20 +68,27 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
     const int part = threadIdx.x % PARTS, col = threadIdx.x / PARTS;
     const int j0 = blockIdx.z * cols;
     const int j = j0 + col;
-    const bool live = j < dv;
-    const int ncols = min(cols, dv - j0);
-    const int off_v = (decay_kind == 0 ? 2 : 3) * DKP, off_s = off_v + colsp;
+    const bool max_gate = !DELTA && decay_kind == 2;
+    const int dvx = max_gate ? dv + 1 : dv;               // with the normaliser as one more column
+    const bool live = j < dvx;
+    const bool is_norm = max_gate && j == dv;
+    const int ncols = min(cols, dvx - j0);
+    const int off_v = (decay_kind == 1 ? 3 : 2) * DKP, off_s = off_v + colsp;
     const int rl = off_s + 4;
     const int hq = h / (heads / qk_heads);
-    float* st = state + ((long long)state_slot[r] * heads + h) * dk * dv;
+    const long long slot_head = (long long)state_slot[r] * heads + h;
+    float* st = state + slot_head * dk * dv;
+    float* nst = max_gate ? mg.nstate + slot_head * dk : nullptr;
     float s[4 * NG];
 #pragma unroll
     for (int ig = 0; ig < NG; ++ig)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int i = 4 * (ig * PARTS + part) + e;
-            s[4 * ig + e] = (live && i < dk) ? st[(long long)i * dv + j] : 0.f;
+            s[4 * ig + e] = (live && i < dk) ? (is_norm ? nst[i] : st[(long long)i * dv + j]) : 0.f;
         }
+    float m_run = (max_gate && threadIdx.x == 0) ? mg.mstate[slot_head * (dv + 1) + j0] : 0.f;
+    const float bias_i = max_gate ? mg.i_bias[h] : 0.f, bias_f = max_gate ? mg.f_bias[h] : 0.f;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const float neg_rate = decay_kind == 0 ? -expf(A_log[h]) : 0.f;
@@ -87,9 +113,15 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                 }
             }
             const float* vsrc = v + t * ldv + h * dv + j0;
-            for (int c = lane; c < ncols; c += 32) copy_async4(row + off_v + c, vsrc + c);
-            if (decay_kind == 0) {
-                if (lane == 0) copy_async4(row + off_s, dec + t * ldd + h);
+            for (int c = lane; c < ncols; c += 32) {
+                if (j0 + c < dv) copy_async4(row + off_v + c, vsrc + c);
+                else row[off_v + c] = 1.0f;                // the normaliser's column takes k itself
+            }
+            if (decay_kind != 1) {
+                if (lane == 0) {
+                    copy_async4(row + off_s, dec + t * ldd + h);
+                    if (max_gate) copy_async4(row + off_s + 1, mg.igate + t * mg.ldi + h);
+                }
             } else {
                 const float* dsrc = dec + t * ldd + h * dk;
 #pragma unroll
@@ -108,6 +140,29 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
         const int n = min(tile, t1 - first);
         float* const cur = which ? buf1 : buf0;
         copy_async_wait_all();
+        if (max_gate) {
+            // log gates of the tile's tokens (a warp a token: its lane 0 issued both copies), then the running
+            // maxima in token order by one thread: slots of a row become [f, i, m', f + m - m']
+            for (int tok = warp; tok < n; tok += nwarp) {
+                float* row = cur + (size_t)tok * rl;
+                if (lane == 0) {
+                    row[off_s] = log_sigmoid_g(mg.cap * tanhf((row[off_s] + bias_f) / mg.cap));
+                    row[off_s + 1] = mg.cap * tanhf((row[off_s + 1] + bias_i) / mg.cap);
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int tok = 0; tok < n; ++tok) {
+                    float* row = cur + (size_t)tok * rl;
+                    const float carried = row[off_s] + m_run;
+                    const float m_new = fmaxf(carried, row[off_s + 1]);
+                    row[off_s + 2] = m_new;
+                    row[off_s + 3] = carried - m_new;
+                    m_run = m_new;
+                }
+            }
+            __syncthreads();
+        }
         for (int tok = warp; tok < n; tok += nwarp) {      // lengths, decays and write strengths of the tile
             float* row = cur + (size_t)tok * rl;
             float qv[DKP / 32 > 0 ? DKP / 32 : 1], kv[DKP / 32 > 0 ? DKP / 32 : 1];
@@ -121,20 +176,23 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                 sk = fmaf(kv[ii], kv[ii], sk);
                 skq = fmaf(qv[ii], kv[ii], skq);
             }
-            if (decay_kind == 0) {
+            float fq = q_scale, fk = 1.0f;
+            if (max_gate) {
+                fk = expf(row[off_s + 1] - row[off_s + 2]);               // the write strength exp(i - m') rides on k
+                if (lane == 0) row[off_s] = expf(row[off_s + 3]);         // the decay exp(f + m - m')
+            } else if (decay_kind == 0) {
                 if (lane == 0) row[off_s] = expf(neg_rate * softplus_g(row[off_s] + bias0));
             } else {
 #pragma unroll
                 for (int i = lane; i < DKP; i += 32)
                     row[2 * DKP + i] = i < dk ? expf(-softplus_g(-row[2 * DKP + i]) * inv_tau) : 1.0f;
             }
-            if (lane == 1) row[off_s + 1] = DELTA ? sigmoid_g(row[off_s + 1]) : 0.f;
-            float fq = q_scale, fk = 1.0f;
+            if (lane == 1 && !max_gate) row[off_s + 1] = DELTA ? sigmoid_g(row[off_s + 1]) : 0.f;
             if (unit) {
                 sq = warp_sum(sq);
                 sk = warp_sum(sk);
                 fq = q_scale * (1.0f / sqrtf(sq + unit_eps));
-                fk = 1.0f / sqrtf(sk + unit_eps);
+                fk *= 1.0f / sqrtf(sk + unit_eps);
             }
             if (DELTA) {
                 skq = warp_sum(skq);
@@ -205,7 +263,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
                     const int g = ig * PARTS + part;
                     kk[ig] = k4[g];
                     const float4 qq = q4[g];
-                    if (decay_kind == 0) {
+                    if (decay_kind != 1) {
                         s[4 * ig] *= sc.x; s[4 * ig + 1] *= sc.x; s[4 * ig + 2] *= sc.x; s[4 * ig + 3] *= sc.x;
                     } else {
                         const float4 a = a4[g];
@@ -224,7 +282,12 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
 #pragma unroll
                 for (int x = PARTS >> 1; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
             }
-            if (live && part == 0) o[(long long)(first + tok) * ldo + h * dv + j] = acc;
+            if (live && part == 0) {
+                if (is_norm)
+                    mg.rden[(long long)(first + tok) * heads + h] = 1.0f / (fmaxf(fabsf(acc), expf(-sc.z)) + mg.den_eps);
+                else
+                    o[(long long)(first + tok) * ldo + h * dv + j] = acc;
+            }
         }
     }
 #pragma unroll
@@ -232,8 +295,13 @@ __global__ void gated_scan_kernel(const float* __restrict__ q, int ldq, const fl
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int i = 4 * (ig * PARTS + part) + e;
-            if (live && i < dk) st[(long long)i * dv + j] = s[4 * ig + e];
+            if (live && i < dk) {
+                if (is_norm) nst[i] = s[4 * ig + e];
+                else st[(long long)i * dv + j] = s[4 * ig + e];
+            }
         }
+    if (max_gate && threadIdx.x == 0)
+        for (int c = 0; c < ncols; ++c) mg.mstate[slot_head * (dv + 1) + j0 + c] = m_run;
 }
 
 // ------------------------------------------------------------------- per-head norms, rotation, paged write
@@ -433,17 +501,14 @@ __global__ void add_vec_rows_kernel(float* x, const float* x0, const float* __re
 
 }  // namespace
 
-void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* dec, int ldd,
-                const float* beta, int ldb, const float* A_log, const float* dec_bias, float* state,
-                const int32_t* cu_q, const int32_t* state_slot, float* o, int ldo, int R, int heads, int qk_heads,
-                int dk, int dv, int unit, float unit_eps, float q_scale, int decay_kind, float tau,
-                cudaStream_t stream) {
-    if (R <= 0) return;
-    DLM_CHECK(dk >= 1 && dk <= 512 && dv >= 1, "gated_scan: key size 1..512");
-    DLM_CHECK(qk_heads >= 1 && heads % qk_heads == 0, "gated_scan: heads must be a multiple of the query/key heads");
-    DLM_CHECK(decay_kind == 0 || decay_kind == 1, "gated_scan: decay kind 0 (per head) or 1 (per key channel)");
-    DLM_CHECK(decay_kind == 1 || A_log != nullptr, "gated_scan: a decay per head needs its rates");
-    DLM_CHECK(decay_kind == 0 || tau > 0.f, "gated_scan: tau must be positive");
+namespace {
+
+void launch_gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* dec,
+                       int ldd, const float* beta, int ldb, const float* A_log, const float* dec_bias, float* state,
+                       const int32_t* cu_q, const int32_t* state_slot, float* o, int ldo, int R, int heads,
+                       int qk_heads, int dk, int dv_own, int unit, float unit_eps, float q_scale, int decay_kind,
+                       float tau, MaxGateArgs mg, cudaStream_t stream) {
+    const int dv = decay_kind == 2 ? dv_own + 1 : dv_own;    // columns the blocks share out (the normaliser is one)
     // rows a lane keeps: 4 NG, over PARTS lanes a column (short chains for small heads)
     const int ng = dk <= 64 ? 1 : (dk <= 256 ? 2 : 4);
     const int parts = dk <= 16 ? 4 : (dk <= 32 ? 8 : (dk <= 128 ? 16 : 32));
@@ -452,7 +517,7 @@ void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v
     while (cols > 1 && cols / 2 >= dv) cols /= 2;           // no more columns than the head has (a power of two)
     if (cols * parts < 32) cols = 32 / parts;                // at least a warp
     const int chunks = (dv + cols - 1) / cols;
-    const int rl = (decay_kind == 0 ? 2 : 3) * dkp + ((cols + 3) & ~3) + 4;
+    const int rl = (decay_kind == 1 ? 3 : 2) * dkp + ((cols + 3) & ~3) + 4;
     int tile = (23 * 1024) / (rl * (int)sizeof(float));     // two buffers within 48 KB
     tile = tile < 1 ? 1 : (tile > 32 ? 32 : tile);
     const size_t smem = (size_t)2 * tile * rl * sizeof(float);
@@ -460,8 +525,8 @@ void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v
     const float inv_tau = decay_kind == 1 ? 1.0f / tau : 0.f;
 #define DLM_GSCAN(NG, PARTS, DELTA)                                                                                 \
     gated_scan_kernel<NG, PARTS, DELTA><<<grid, cols * parts, smem, stream>>>(q, ldq, k, ldk, v, ldv, dec, ldd,     \
-        beta, ldb, A_log, dec_bias, state, cu_q, state_slot, o, ldo, heads, qk_heads, dk, dv, unit, unit_eps,       \
-        q_scale, decay_kind, inv_tau, tile)
+        beta, ldb, A_log, dec_bias, state, cu_q, state_slot, o, ldo, heads, qk_heads, dk, dv_own, unit, unit_eps,   \
+        q_scale, decay_kind, inv_tau, tile, mg)
 #define DLM_GSCAN_SIZES(DELTA)                                                                                      \
     do {                                                                                                            \
         if (dkp == 16) DLM_GSCAN(1, 4, DELTA);                                                                      \
@@ -476,6 +541,37 @@ void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v
 #undef DLM_GSCAN_SIZES
 #undef DLM_GSCAN
     check_launch("gated_scan");
+}
+
+}  // namespace
+
+void gated_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* dec, int ldd,
+                const float* beta, int ldb, const float* A_log, const float* dec_bias, float* state,
+                const int32_t* cu_q, const int32_t* state_slot, float* o, int ldo, int R, int heads, int qk_heads,
+                int dk, int dv, int unit, float unit_eps, float q_scale, int decay_kind, float tau,
+                cudaStream_t stream) {
+    if (R <= 0) return;
+    DLM_CHECK(dk >= 1 && dk <= 512 && dv >= 1, "gated_scan: key size 1..512");
+    DLM_CHECK(qk_heads >= 1 && heads % qk_heads == 0, "gated_scan: heads must be a multiple of the query/key heads");
+    DLM_CHECK(decay_kind == 0 || decay_kind == 1, "gated_scan: decay kind 0 (per head) or 1 (per key channel)");
+    DLM_CHECK(decay_kind == 1 || A_log != nullptr, "gated_scan: a decay per head needs its rates");
+    DLM_CHECK(decay_kind == 0 || tau > 0.f, "gated_scan: tau must be positive");
+    launch_gated_scan(q, ldq, k, ldk, v, ldv, dec, ldd, beta, ldb, A_log, dec_bias, state, cu_q, state_slot, o, ldo, R,
+                      heads, qk_heads, dk, dv, unit, unit_eps, q_scale, decay_kind, tau, MaxGateArgs{}, stream);
+}
+
+void memory_scan(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* igate, int ldi,
+                 const float* fgate, int ldf, const float* i_bias, const float* f_bias, float cap, float* state,
+                 float* nstate, float* mstate, const int32_t* cu_q, const int32_t* state_slot, float* o, int ldo,
+                 float* rden, int R, int heads, int dk, int dv, float q_scale, float den_eps, cudaStream_t stream) {
+    if (R <= 0) return;
+    DLM_CHECK(dk >= 1 && dk <= 512 && dv >= 1, "memory_scan: key size 1..512");
+    DLM_CHECK(cap > 0.f, "memory_scan: the gates' cap must be positive");
+    DLM_CHECK(i_bias != nullptr && f_bias != nullptr && nstate != nullptr && mstate != nullptr && rden != nullptr,
+              "memory_scan: gate biases, normaliser, maximum and the denominators' place are needed");
+    const MaxGateArgs mg{igate, ldi, i_bias, f_bias, cap, den_eps, nstate, mstate, rden};
+    launch_gated_scan(q, ldq, k, ldk, v, ldv, fgate, ldf, nullptr, 0, nullptr, nullptr, state, cu_q, state_slot, o, ldo,
+                      R, heads, heads, dk, dv, 0, 0.f, q_scale, 2, 0.f, mg, stream);
 }
 
 void head_norm_rope_write(const float* qkv, int ld, const int32_t* positions, const float* qn_w, const float* kn_w,

@@ -260,7 +260,7 @@ __device__ __forceinline__ void select_token(float* prob, const float* logits, i
         __syncwarp();
     }
     if (lane == 0) {
-        const float div = (norm && chosen_sum > 0.f) ? chosen_sum : 1.0f;
+        const float div = (norm && chosen_sum > 0.f) ? (norm == 2 ? chosen_sum + 1e-20f : chosen_sum) : 1.0f;
         if (div != 1.0f || scale != 1.0f)
             for (int j = 0; j < k; ++j) wts[t * k + j] = (wts[t * k + j] / div) * scale;
     }

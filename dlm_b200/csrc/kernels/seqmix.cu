@@ -254,13 +254,31 @@ __global__ void table_lookup_kernel(const int32_t* __restrict__ tokens, const in
 // mode 1: out = y / rms(y) * w * sigmoid(gate).  rms over the group, eps inside the root.
 template <typename TOut>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gate, int ldg,
-                                     const float* __restrict__ w, TOut* out, int ldo, int gs, float eps, int mode) {
+                                     const float* __restrict__ w, TOut* out, int ldo, int gs, float eps, int mode,
+                                     const float* row_scale) {
     dep_wait();          // nothing is read or written before the kernels before this one have ended
     dep_launch_next();
     __shared__ float s_part[32];
     const int t = blockIdx.x, g = blockIdx.y;
     const float* yr = y + (long long)t * ldy + (long long)g * gs;
     const float* gr = gate + (long long)t * ldg + (long long)g * gs;
+    if (row_scale != nullptr) {
+        // y is first multiplied by a factor per (token, group); the norm's eps then meets the scaled values
+        const float f = row_scale[(long long)t * gridDim.y + g];
+        float part = 0.f;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            const float v = yr[i] * f;
+            part = fmaf(v, v, part);
+        }
+        const float inv = 1.0f / sqrtf(block_sum(part, s_part) / (float)gs + eps);
+        TOut* o = out + (long long)t * ldo + (long long)g * gs;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            const float wi = w != nullptr ? w[(long long)g * gs + i] : 1.0f;
+            const float v = ((yr[i] * f) * inv) * wi;
+            o[i] = from_f32<TOut>(mode == 1 ? v * sigmoid_f(gr[i]) : v * silu_f(gr[i]));
+        }
+        return;
+    }
     float part = 0.f;
     for (int i = threadIdx.x; i < gs; i += blockDim.x) {
         const float v = mode == 0 ? yr[i] * silu_f(gr[i]) : yr[i];
@@ -724,15 +742,17 @@ void table_lookup(const int32_t* tokens, const int32_t* table, int32_t* ids, flo
 }
 
 void gated_rmsnorm(const float* y, int ldy, const float* gate, int ldg, const float* w, void* out, int ldo, int T,
-                   int groups, int group_size, float eps, int mode, int out_dtype, cudaStream_t stream) {
+                   int groups, int group_size, float eps, int mode, int out_dtype, const float* row_scale,
+                   cudaStream_t stream) {
     if (T <= 0) return;
+    DLM_CHECK(row_scale == nullptr || mode != 0, "gated_rmsnorm: a factor per row goes with a gate after the norm");
     const int threads = group_size >= 256 ? 256 : (group_size >= 128 ? 128 : (group_size > 32 ? 64 : 32));
     if (out_dtype == F32)
         launch_dep(gated_rmsnorm_kernel<float>, dim3(T, groups), dim3(threads), 0, stream, y, ldy, gate, ldg, w, static_cast<float*>(out),
-                                                                          ldo, group_size, eps, mode);
+                                                                          ldo, group_size, eps, mode, row_scale);
     else
         launch_dep(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(T, groups), dim3(threads), 0, stream, 
-            y, ldy, gate, ldg, w, static_cast<__nv_bfloat16*>(out), ldo, group_size, eps, mode);
+            y, ldy, gate, ldg, w, static_cast<__nv_bfloat16*>(out), ldo, group_size, eps, mode, row_scale);
     check_launch("gated_rmsnorm");
 }
 

@@ -185,16 +185,19 @@ class NativeOps:
         self.k.activation(_p(x), x.stride(0), _p(out), C, R, C, self._ACTS[op], _dt(out_dtype), self._stream())
         return out
 
-    def gated_rmsnorm(self, y, gate, w, groups, eps, mode, out_dtype):
+    def gated_rmsnorm(self, y, gate, w, groups, eps, mode, out_dtype, row_scale=None):
         """Norm over ``groups`` equal parts of the channels with a gate; ``mode`` ``"silu_before"``:
-        ``rms(y * silu(gate)) * w``; ``"sigmoid_after"``: ``rms(y) * w * sigmoid(gate)``."""
+        ``rms(y * silu(gate)) * w``; ``"sigmoid_after"``: ``rms(y) * w * sigmoid(gate)``.  ``row_scale`` (32-bit
+        ``[T, groups]``, with a gate after the norm): y is multiplied by it first, group by group."""
         T, C = y.shape
         assert C % groups == 0 and gate.shape == (T, C) and y.stride(1) == 1 and gate.stride(1) == 1
+        assert row_scale is None or (row_scale.shape == (T, groups) and row_scale.is_contiguous()
+                                     and row_scale.dtype == torch.float32 and mode != "silu_before")
         out = torch.empty((T, C), dtype=out_dtype, device=y.device)
         self.launches += 1
         self.k.gated_rmsnorm(_p(y), y.stride(0), _p(gate), gate.stride(0), _p(w), _p(out), C, T, groups, C // groups,
                              float(eps), {"silu_before": 0, "sigmoid_after": 1, "silu_after": 2}[mode], _dt(out_dtype),
-                             self._stream())
+                             _p(row_scale), self._stream())
         return out
 
     def ssm_scan(self, xbc, dt_raw, dt_bias, A_log, D, state, batch, heads, P, N, groups, fixed_decay=None):
@@ -390,6 +393,70 @@ class NativeOps:
         self.launches += 1
         self.k.add_vec_rows(_p(x), _p(x0), _p(vec), T, H, self._stream())
 
+    # ------------------------------------- squashing norms and caps, a gate per entry, the max-gated matrix memory
+    def dyt_norm(self, x, w, b, alpha, out_dtype, rows=None):
+        """``tanh(alpha * x) * w + b`` of the 32-bit rows x (only ``rows`` of them when given) in ``out_dtype``."""
+        H = x.shape[-1]
+        assert x.dtype == torch.float32 and x.is_contiguous() and w.shape == (H,) and b.shape == (H,)
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, H), dtype=out_dtype, device=x.device)
+        self.launches += 1
+        self.k.dyt_norm(_p(x), _p(rows), _p(w), _p(b), float(alpha), _p(out), n, H, _dt(out_dtype), self._stream())
+        return out
+
+    def dyt_norm_pair(self, x, wa, ba, alpha_a, wb, bb, alpha_b, out_dtype, want_f32=False):
+        """The same 32-bit rows through two such norms in one pass; with ``want_f32`` the second result also in
+        32-bit: ``(a, b, b32 or None)``."""
+        T, H = x.shape
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        a = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        b = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        b32 = torch.empty((T, H), dtype=torch.float32, device=x.device) if want_f32 and out_dtype != torch.float32 else None
+        self.launches += 1
+        self.k.dyt_norm_pair(_p(x), _p(wa), _p(ba), float(alpha_a), _p(a), _p(wb), _p(bb), float(alpha_b), _p(b), _p(b32),
+                             T, H, _dt(out_dtype), self._stream())
+        return a, b, (b if want_f32 and b32 is None else b32)
+
+    def tanh_cap(self, x, cap):
+        """``x <- cap * tanh(x / cap)`` in place on a contiguous 32-bit tensor."""
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        self.launches += 1
+        self.k.tanh_cap(_p(x), x.numel(), float(cap), self._stream())
+
+    def entry_gate(self, o, gate, nh, dv, D, factor=1.0):
+        """``o[t, h * D + i] *= factor * sigmoid(gate[t, h * dv + i])`` for ``i < dv``, in place (``gate`` 32-bit,
+        may be a column slice; heads stored ``D`` wide keep their padding)."""
+        T = o.shape[0]
+        assert o.shape[1] == nh * D and o.is_contiguous() and gate.dtype == torch.float32
+        assert gate.shape == (T, nh * dv) and gate.stride(1) == 1
+        self.launches += 1
+        self.k.entry_gate(_p(o), _p(gate), gate.stride(0), T, nh, dv, D, float(factor), _dt(o.dtype), self._stream())
+
+    def memory_scan(self, q, k, v, igate, fgate, i_bias, f_bias, cap, S, n, m, batch, heads, dk, dv, q_scale=1.0,
+                    den_eps=1e-6):
+        """Matrix memory with exponential gates and a running maximum over each request's tokens: with
+        ``i = cap tanh((igate + i_bias) / cap)``, ``f = log sigmoid(cap tanh((fgate + f_bias) / cap))``:
+        ``m' = max(f + m, i)``; ``S <- exp(f + m - m') S + exp(i - m') k v^T``; n likewise with k alone;
+        ``o = S^T q`` (q times ``q_scale``).  ``q, k [T, heads * dk]``, ``v [T, heads * dv]``, ``igate, fgate
+        [T, heads]``, all 32-bit and possibly column slices.  ``S [slots, heads, dk, dv]``, ``n [slots, heads, dk]``
+        and ``m [slots, heads, dv + 1]`` (equal copies of the maximum) are read and left up to date.  Returns o
+        ``[T, heads * dv]`` (not divided) and ``1 / (max(|n . q|, exp(-m')) + den_eps)`` ``[T, heads]``."""
+        T = v.shape[0]
+        for t in (q, k, v, igate, fgate):
+            assert t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == T
+        assert q.shape[1] == heads * dk and k.shape[1] == heads * dk and v.shape[1] == heads * dv
+        assert igate.shape[1] == heads and fgate.shape[1] == heads
+        assert S.shape[1:] == (heads, dk, dv) and n.shape[1:] == (heads, dk) and m.shape[1:] == (heads, dv + 1)
+        assert S.dtype == n.dtype == m.dtype == torch.float32
+        o = torch.empty((T, heads * dv), dtype=torch.float32, device=v.device)
+        rden = torch.empty((T, heads), dtype=torch.float32, device=v.device)
+        self.launches += 1
+        self.k.memory_scan(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(igate), igate.stride(0),
+                           _p(fgate), fgate.stride(0), _p(i_bias), _p(f_bias), float(cap), _p(S), _p(n), _p(m),
+                           _p(batch.cu_q), _p(batch.state_slot), _p(o), heads * dv, _p(rden), batch.num_requests, heads,
+                           dk, dv, float(q_scale), float(den_eps), self._stream())
+        return o, rden
+
     def head_offsets(self, H, T, device):
         """``[0, T, 2T, ..., H T]``: the groups of a grouped product whose groups are heads (kept: built once)."""
         key = (H, T, str(device))
@@ -548,10 +615,11 @@ class NativeOps:
         return q
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len, num_single=0, slopes=None, chunk=0, sinks=None):
+                  max_kv_len, num_single=0, slopes=None, chunk=0, sinks=None, softcap=0.0):
         """``slopes`` (32-bit ``[nh]`` or None): a score loses ``slopes[head] * (query position - key position)``.
         ``chunk`` > 0: a query at p sees only keys from ``floor(p / chunk) * chunk`` on.  ``sinks`` (32-bit ``[nh]`` or
-        None): the softmax's denominator also holds ``exp(sinks[head])``."""
+        None): the softmax's denominator also holds ``exp(sinks[head])``.  ``softcap`` c > 0: the scaled dot product
+        becomes ``c tanh(. / c)`` first."""
         T = q.shape[0]
         R, width = block_table.shape
         total_pages, _, page_size, _ = k_cache.shape
@@ -566,7 +634,7 @@ class NativeOps:
         self.launches += 1 if scratch is None else (decode_kernels if num_single == R else decode_kernels + 1)
         self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
                          nh, nkv, hd, page_size, total_pages, int(window), float(scale), _p(slopes), int(chunk), _p(sinks),
-                         int(max_q_len), int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast,
+                         float(softcap), int(max_q_len), int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast,
                          self._stream())
         return out
 
@@ -631,11 +699,16 @@ class NativeOps:
         self.k.moe_permute(_p(ids), n, k, E, _p(offsets), _p(rows), _p(dest), self._stream())
         return offsets, rows, dest
 
-    def moe_combine(self, y, dest, wts, shared, gate, resid):
+    def moe_combine(self, y, dest, wts, shared, gate, resid, ids=None, num_real=0, passthrough=None, shared_scale=1.0):
+        """``resid[t] += sum_j wts[t, j] y[dest[t, j]] + shared_scale * gate[t] * shared[t]`` (no gate: 1).  With
+        ``ids``: a pair whose expert id is ``num_real`` or more reads ``passthrough[t]`` (32-bit ``[T, H]``) instead of
+        a row of y (``y`` may be None when there are no other experts)."""
         T, H = resid.shape
+        assert ids is None or (passthrough is not None and passthrough.shape == (T, H) and passthrough.is_contiguous()
+                               and passthrough.dtype == torch.float32 and ids.shape == dest.shape)
         self.launches += 1
-        self.k.moe_combine(_p(y), _p(dest), _p(wts), _p(shared), _p(gate), _p(resid), T, H, dest.shape[1],
-                           self._stream())
+        self.k.moe_combine(_p(y), _p(dest), _p(wts), _p(shared), _p(gate), _p(resid), T, H, dest.shape[1], _p(ids),
+                           int(num_real), _p(passthrough), float(shared_scale), self._stream())
 
     # -------------------------------------------------------------- sampling
     def argmax(self, logits):

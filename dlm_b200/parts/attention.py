@@ -264,16 +264,20 @@ class NormedBiasedAttention(Mixer):
 class HeadNormedAttention(Mixer):
     """Grouped-query softmax attention with a norm per head, a choice of masks, an optional sink and an optional gate.
 
-    ``q, k, v = W h`` (no biases) with ``heads`` query heads and ``kv_heads`` key/value heads (query head n reads
-    key/value head ``n // (heads / kv_heads)``), keys ``dim`` wide, values ``vdim`` wide.  With ``qk_norm`` every query
+    ``q, k, v = W h`` (with ``qkv_bias`` plus the biases ``q.b``, ``k.b``, ``v.b``, added in the projection) with
+    ``heads`` query heads and ``kv_heads`` key/value heads (query head n reads key/value head
+    ``n // (heads / kv_heads)``), keys ``dim`` wide, values ``vdim`` wide.  With ``qk_norm`` every query
     head is divided by its root mean square over ``dim`` and multiplied by ``q.norm`` (``[dim]``, the same for all
     heads), every key head likewise with ``k.norm``; then the rotation (``position``: any registered rotary encoding;
-    its table, how many entries it turns and how it pairs them are the encoding's).  A score is ``(q . k) * scale``.
+    its table, how many entries it turns and how it pairs them are the encoding's).  A score is ``(q . k) * scale``,
+    and with ``softcap`` c then ``c tanh(score / c)``.
     A query at p sees key ``j <= p`` iff ``p - j < window`` (when a window is given) and
     ``floor(j / chunk) == floor(p / chunk)`` (when a chunk size is given; chunks are counted from position 0 of the
     request).  With ``sink`` the softmax's denominator also holds ``exp(sink_n)``, a learned logit per head that has
-    no key and no value and is not scaled.  With ``gate`` head n's output is multiplied by ``sigmoid(W_g h)_n``.
-    The output is ``out_scale * W_o [heads side by side]``.
+    no key and no value and is not scaled.  ``gate`` True or ``"head"``: head n's output is multiplied by
+    ``sigmoid(W_g h)_n`` (``g`` is ``[heads, hidden]``); ``"entry"``: the heads side by side are multiplied entry by
+    entry by ``sigmoid(W_g h)`` (``g`` is ``[heads * vdim, hidden]``).  The gate reads the same input as the
+    projections.  The output is ``out_scale * (W_o [heads side by side] + o.b)`` (the bias with ``o_bias``).
 
     Keys and values are cached with one head size (the larger of ``dim`` and ``vdim``, rounded up to a size the
     tensor-core kernels take; zeros beyond a head's own, zero columns in ``W_o``).  A chunked mask never looks back
@@ -284,34 +288,50 @@ class HeadNormedAttention(Mixer):
 
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float,
                  qk_norm: bool = True, position: PartSpec | None = None, window: int | None = None,
-                 chunk: int | None = None, sink: bool = False, gate: bool = False, out_scale: float = 1.0):
+                 chunk: int | None = None, sink: bool = False, gate: bool | str = False, out_scale: float = 1.0,
+                 qkv_bias: bool = False, o_bias: bool = False, softcap: float | None = None):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
+        if gate not in (False, True, "head", "entry"):
+            raise ValueError(f"gate must be False, True, 'head' or 'entry', got {gate!r}")
         self.hidden, self.H, self.G, self.d, self.dv = int(hidden_size), int(heads), int(kv_heads), int(dim), int(vdim)
         self.scale, self.eps, self.out_scale = float(scale), float(eps), float(out_scale)
         self.qk_norm, self.has_sink, self.has_gate = bool(qk_norm), bool(sink), bool(gate)
+        self.gate_rows = self.H * self.dv if gate == "entry" else self.H          # rows of W_g
+        self.qkv_bias, self.o_bias = bool(qkv_bias), bool(o_bias)
+        self.softcap = float(softcap) if softcap else 0.0
         self.window = int(window) if window else None
         self.chunk = int(chunk) if chunk else None
         self.position = build_part("position", position) if position is not None else None
         need = max(self.d, self.dv)
         self.D = next((s for s in self._HEAD_SIZES if s >= need), -(-need // 8) * 8)
-        self.w_in = self.w_o = self.qn = self.kn = self.sink = None
+        self.w_in = self.b_in = self.w_o = self.b_o = self.qn = self.kn = self.sink = None
 
     def param_specs(self):
         H, G, d, dv = self.H, self.G, self.d, self.dv
         specs = [ParamSpec("q", (H * d, self.hidden)), ParamSpec("k", (G * d, self.hidden)),
                  ParamSpec("v", (G * dv, self.hidden)), ParamSpec("o", (self.hidden, H * dv))]
+        if self.qkv_bias:
+            specs += [ParamSpec("q.b", (H * d,), init="bias"), ParamSpec("k.b", (G * d,), init="bias"),
+                      ParamSpec("v.b", (G * dv,), init="bias")]
+        if self.o_bias:
+            specs.append(ParamSpec("o.b", (self.hidden,), init="bias"))
         if self.qk_norm:
             specs += [ParamSpec("q.norm", (d,), init="norm"), ParamSpec("k.norm", (d,), init="norm")]
         if self.has_sink:
             specs.append(ParamSpec("sink", (H,), init="bias"))
         if self.has_gate:
-            specs.append(ParamSpec("g", (H, self.hidden)))
+            specs.append(ParamSpec("g", (self.gate_rows, self.hidden)))
         return specs
 
     def load(self, tensors, rt: Runtime):
         names = ("q", "k", "v", "g") if self.has_gate else ("q", "k", "v")
         self.w_in = torch.cat([rt.matrix(tensors[n]) for n in names], dim=0).contiguous()
+        if self.qkv_bias:       # the gate has no bias: zeros for its rows
+            parts = [rt.vector(tensors[n + ".b"]) for n in "qkv"]
+            if self.has_gate:
+                parts.append(torch.zeros(self.gate_rows, dtype=torch.float32, device=rt.device))
+            self.b_in = torch.cat(parts).contiguous()
         w_o = tensors["o"].to(device=rt.device, dtype=torch.float32)
         if not self.has_gate and self.out_scale != 1.0:
             w_o = w_o * self.out_scale             # with a gate the factor rides on the gate instead
@@ -320,6 +340,7 @@ class HeadNormedAttention(Mixer):
             wide[:, :, :self.dv] = w_o.reshape(self.hidden, self.H, self.dv)
             w_o = wide.reshape(self.hidden, self.H * self.D)
         self.w_o = rt.matrix(w_o)
+        self.b_o = (rt.vector(tensors["o.b"]) * self.out_scale).contiguous() if self.o_bias else None
         if self.qk_norm:
             self.qn, self.kn = rt.vector(tensors["q.norm"]), rt.vector(tensors["k.norm"])
         self.sink = rt.vector(tensors["sink"]) if self.has_sink else None
@@ -336,18 +357,26 @@ class HeadNormedAttention(Mixer):
         rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
         H, G, d, dv = self.H, self.G, self.d, self.dv
         view = ctx.paged(call)
-        proj = ops.linear(h, self.w_in, None, torch.float32)               # [q | k | v | gate]
+        proj = ops.linear(h, self.w_in, self.b_in, torch.float32)          # [q | k | v | gate]
         rot = self.position.rotary(rt) if self.position is not None else None
         inv_freq, rot_dims = rot if rot is not None else (None, 0)
         q = ops.head_norm_rope_write(proj, b.positions, self.qn, self.kn, self.eps, inv_freq, rot_dims,
                                      bool(rot is not None and self.position.interleaved),
                                      view.group.slots if view.write else None, view.k, view.v, H, G, d, dv, self.D,
                                      rt.dtype)
+        extra = {"softcap": self.softcap} if self.softcap else {}
         o = ops.attention(q, view.k, view.v, view.group.block_table, b.cu_q, b.kv_len, self.window or 0, self.scale,
-                          H, G, self.D, b.max_q_len, b.max_kv_len, b.num_single, chunk=self.chunk or 0, sinks=self.sink)
+                          H, G, self.D, b.max_q_len, b.max_kv_len, b.num_single, chunk=self.chunk or 0, sinks=self.sink,
+                          **extra)
         if self.has_gate:
-            ops.head_gate(o, proj[:, (H + G) * d + G * dv:], H, self.D, self.out_scale)
+            g = proj[:, (H + G) * d + G * dv:]
+            if self.gate_rows == H:
+                ops.head_gate(o, g, H, self.D, self.out_scale)
+            else:
+                ops.entry_gate(o, g, H, dv, self.D, self.out_scale)
         ops.linear_add(o, self.w_o, resid)
+        if self.b_o is not None:
+            ops.add_vec_rows(resid, None, self.b_o)
 
 
 register_part("mixer", "gqa_attention", GroupedQueryAttention)

@@ -34,10 +34,12 @@ class InputInjection(Part):
 
 class AdditiveEntry(Part):
     """Before pass t of a repeated run: ``x <- x + x0 + step[t]`` for t > 0 and ``x <- x + step[0]`` for the first pass,
-    with x0 the embedded tokens and ``step`` ``[passes, hidden]``; all of it 32-bit, in place."""
+    with x0 the embedded tokens and ``step`` ``[passes, hidden]``; all of it 32-bit, in place.  With
+    ``add_embedded`` False the embedded tokens are never added: ``x <- x + step[t]`` in every pass."""
 
-    def __init__(self, hidden_size: int, passes: int, step: str = "step"):
+    def __init__(self, hidden_size: int, passes: int, step: str = "step", add_embedded: bool = True):
         self.hidden, self.passes, self.n_step = int(hidden_size), int(passes), str(step)
+        self.needs_embedded = bool(add_embedded)      # False: the model need not keep the embedded tokens
         self.step = None
 
     def param_specs(self):
@@ -49,7 +51,7 @@ class AdditiveEntry(Part):
     def forward(self, x: torch.Tensor, x0: torch.Tensor, t: int, rt: Runtime) -> torch.Tensor:
         if not (0 <= t < self.passes):
             raise ValueError(f"pass {t} of {self.passes}")
-        rt.ops.add_vec_rows(x, x0 if t > 0 else None, self.step[t])
+        rt.ops.add_vec_rows(x, x0 if (t > 0 and self.needs_embedded) else None, self.step[t])
         return x
 
 

@@ -168,6 +168,82 @@ class SoftmaxTopKMoE(FeedForward):
         ops.moe_combine(y, dest, wts, shared, gate, resid)
 
 
+class RoutedActExperts(FeedForward):
+    """Routed two-matrix experts, some of which hand their input through, and an optional shared expert.
+
+    Router logits ``z = W_router x`` in 32-bit from the 32-bit normalised residual x; scores ``s = softmax(z)`` over
+    all ``experts + identity`` router outputs.  The ``top`` experts with the largest ``s + correction`` are chosen
+    (``correction`` a stored vector; ties: the lower expert); their weights are their scores s divided by the chosen
+    scores' sum (``+ 1e-20``).  Expert e < ``experts`` gives ``down_e · act(up_e · h)`` (no biases; ``activation``
+    "gelu", the exact form, "gelu_tanh" or "silu"); the last ``identity`` router outputs are identity experts without
+    tensors whose output is x itself.  The shared expert (``shared_size`` given) has the same form, runs for every
+    token and is added unweighted.  ``resid += out_scale * (weighted sum + shared)``.  Tensors: ``router``
+    ``[experts + identity, hidden]``, ``correction`` ``[experts + identity]``, ``e<i>.up`` ``[ff, hidden]``,
+    ``e<i>.down`` ``[hidden, ff]``, ``shared.up``, ``shared.down``; the experts are stacked at load."""
+
+    def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, identity: int = 0,
+                 shared_size: int | None = None, activation: str = "gelu", shared_activation: str | None = None,
+                 out_scale: float = 1.0):
+        self.hidden, self.E, self.k, self.I = int(hidden_size), int(num_experts), int(top), int(expert_size)
+        self.ident = int(identity)
+        if not (1 <= self.k <= self.E + self.ident):
+            raise ValueError("top must be in 1..experts + identity")
+        self.Is = int(shared_size) if shared_size else None
+        self.act = activation
+        self.shared_act = shared_activation or activation
+        for a in (self.act, self.shared_act):
+            if a not in ("gelu", "gelu_tanh", "silu"):
+                raise ValueError(f"unknown expert activation {a!r}")
+        self.out_scale = float(out_scale)
+        self.w_router = self.correction = self.w_up = self.w_down = self.ws_up = self.ws_down = None
+
+    def param_specs(self):
+        n = self.E + self.ident
+        specs = [ParamSpec("router", (n, self.hidden)), ParamSpec("correction", (n,), init="bias")]
+        for e in range(self.E):
+            specs += [ParamSpec(f"e{e}.up", (self.I, self.hidden)), ParamSpec(f"e{e}.down", (self.hidden, self.I))]
+        if self.Is:
+            specs += [ParamSpec("shared.up", (self.Is, self.hidden)), ParamSpec("shared.down", (self.hidden, self.Is))]
+        return specs
+
+    def load(self, tensors, rt: Runtime):
+        self.w_router = rt.matrix(tensors["router"])
+        self.correction = rt.vector(tensors["correction"])
+        if self.E:
+            self.w_up = torch.stack([rt.matrix(tensors[f"e{e}.up"]) for e in range(self.E)]).contiguous()
+            self.w_down = torch.stack([rt.matrix(tensors[f"e{e}.down"]) for e in range(self.E)]).contiguous()
+        if self.Is:
+            self.ws_up, self.ws_down = rt.matrix(tensors["shared.up"]), rt.matrix(tensors["shared.down"])
+
+    def forward(self, h, resid, ctx: StepContext, pre_norm=None):
+        ops = ctx.rt.ops
+        shared = None
+        branch = ops.branch(h.shape[0])
+        if self.Is:
+            # the shared expert needs nothing from the router: it may run beside the routed experts
+            with branch:
+                sact = ops.linear_act(h, self.ws_up, self.shared_act)
+                shared = ops.linear(sact, self.ws_down, None, torch.float32)
+        # the router (and the identity experts) read the normalised residual in 32-bit
+        rms = pre_norm.fusable_rms() if pre_norm is not None else None
+        if rms is not None:
+            x = ops.rmsnorm(resid, rms[0], rms[1], torch.float32)
+        elif pre_norm is not None:
+            x = pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)
+        else:
+            x = h if h.dtype == torch.float32 else h.float()
+        n = self.E + self.ident
+        ids, wts, _, offsets, rows, dest = ops.route(x, self.w_router, n, self.k, 2, False, select_bias=self.correction,
+                                                     scale=self.out_scale)
+        y = None
+        if self.E:
+            act = ops.grouped_act(h, self.w_up, offsets, rows, self.act)
+            y = ops.grouped_linear(act, self.w_down, offsets)
+        branch.join()
+        ops.moe_combine(y, dest, wts, shared, None, resid, ids=ids, num_real=self.E, passthrough=x,
+                        shared_scale=self.out_scale)
+
+
 class TableRoutedExperts(FeedForward):
     """A mixture of small two-matrix experts without a router: row ``token id`` of an integer table
     ``[vocab, top]`` names the token's experts (the entries of a row differ), each weighted ``1 / top``:
@@ -206,6 +282,7 @@ class TableRoutedExperts(FeedForward):
 
 
 register_part("ffn", "table_experts", TableRoutedExperts)
+register_part("ffn", "routed_act_experts", RoutedActExperts)
 register_part("ffn", "swiglu_dense", DenseSwiGLU)
 register_part("ffn", "dense_act", DenseActMLP)
 register_part("ffn", "moe_softmax_topk", SoftmaxTopKMoE)

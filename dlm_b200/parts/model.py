@@ -41,6 +41,7 @@ class ModelSpec:
     residual_streams: int | None = None      # S: blocks get ``[T, S, hidden]`` (S equal copies at the start, summed at the end)
     pass_entry: PartSpec | None = None       # what makes the input of a repeated run's pass (calls with ``enters_pass``)
     pass_entry_prefix: str = ""              # tensor-name prefix of that part's tensors
+    logit_softcap: float = 0.0               # c > 0: the logits are ``c tanh(head product / c)``
 
 
 class WeightError(ValueError):
@@ -175,7 +176,7 @@ class DecoderModel:
         if s.residual_streams is not None:
             x = ops.streams_expand(x, s.residual_streams)
         # a model with repeated passes keeps the embedded tokens: blocks change x in place
-        x0 = x.clone() if self.pass_entry is not None else None
+        x0 = x.clone() if self.pass_entry is not None and getattr(self.pass_entry, "needs_embedded", True) else None
         for ci, c in enumerate(self.order):
             if c.enters_pass is not None:
                 x = self.pass_entry.forward(x, x0, c.enters_pass, rt)
@@ -185,4 +186,7 @@ class DecoderModel:
         if s.residual_streams is not None:
             x = ops.streams_reduce(x, None, None, 0.0, torch.float32)
         n = self.final_norm.forward(x, rt, rows=batch.logit_rows)
-        return ops.linear(n, self.lm_head, None, torch.float32)
+        logits = ops.linear(n, self.lm_head, None, torch.float32)
+        if s.logit_softcap > 0.0:
+            ops.tanh_cap(logits, s.logit_softcap)
+        return logits

@@ -33,4 +33,27 @@ class RMSNorm(Norm):
         return self.weight, self.eps
 
 
+class DynamicTanh(Norm):
+    """A norm that takes no statistics: ``out = tanh(alpha * x) * weight + bias`` entry by entry, with one learned
+    scalar ``alpha``; all of it 32-bit, the result stored in the activation dtype.  Tensors: the weight (``param``),
+    ``<param>.b`` and ``<param>.alpha`` (a tensor without dimensions)."""
+
+    def __init__(self, size: int, param: str = "weight"):
+        self.size, self.param = int(size), str(param)
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def param_specs(self):
+        return [ParamSpec(self.param, (self.size,), init="norm"), ParamSpec(self.param + ".b", (self.size,), init="bias"),
+                ParamSpec(self.param + ".alpha", (), init="norm")]
+
+    def load(self, tensors, rt: Runtime):
+        self.weight, self.bias = rt.vector(tensors[self.param]), rt.vector(tensors[self.param + ".b"])
+        self.alpha = float(tensors[self.param + ".alpha"].to(torch.float32).reshape(()))
+
+    def forward(self, x, rt: Runtime, rows=None, out_dtype=None):
+        return rt.ops.dyt_norm(x, self.weight, self.bias, self.alpha, out_dtype or rt.dtype, rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

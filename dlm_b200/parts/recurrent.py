@@ -338,6 +338,60 @@ class GatedLinearAttention(Mixer):
         ops.linear_add(g, self.w_o, resid)
 
 
+class MatrixMemory(Mixer):
+    """A matrix memory per head with exponential input gates, kept in range by a running maximum of the log gates.
+    ``q = W h * dim^(-1/2)``, ``k = W h`` (heads x dim), ``v = W h`` (heads x vdim), no biases.  Per head a log input
+    gate ``i = c tanh((W_i h + i.b) / c)`` and a log forget gate ``f = log sigmoid(c tanh((W_f h + f.b) / c))`` with
+    ``c = gate_cap``.  With S, n and the running maximum m all zero at the start::
+
+        m' = max(f + m, i);   S <- exp(f + m - m') S + exp(i - m') k v^T;   n <- exp(f + m - m') n + exp(i - m') k
+        o = S^T q / (max(|n . q|, exp(-m')) + den_eps)                    (S: dim x vdim, n: dim; 32-bit)
+
+    Each head's o is divided by its root mean square over ``vdim``; the heads side by side are multiplied by ``norm``
+    (``[heads * vdim]``) and by ``sigmoid(W_g h)``; the output is ``out_scale * W_o`` of that.  A request's state: S, n
+    and m of every head (m in ``vdim + 1`` equal copies, so that every block of the scan kernel, which shares out the
+    columns of ``[S | n]``, carries one of its own).  Everything between the two projections is 32-bit."""
+
+    def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, gate_cap: float, eps: float,
+                 den_eps: float = 1e-6, out_scale: float = 1.0):
+        self.hidden, self.H, self.d, self.dv = int(hidden_size), int(heads), int(dim), int(vdim)
+        self.cap, self.eps, self.den_eps, self.out_scale = float(gate_cap), float(eps), float(den_eps), float(out_scale)
+        if self.cap <= 0:
+            raise ValueError("gate_cap must be positive")
+        self.w_in = self.i_bias = self.f_bias = self.norm_w = self.w_o = None
+
+    def param_specs(self):
+        H, d, dv, hid = self.H, self.d, self.dv, self.hidden
+        return [ParamSpec("q", (H * d, hid)), ParamSpec("k", (H * d, hid)), ParamSpec("v", (H * dv, hid)),
+                ParamSpec("g", (H * dv, hid)), ParamSpec("i", (H, hid)), ParamSpec("i.b", (H,), init="bias"),
+                ParamSpec("f", (H, hid)), ParamSpec("f.b", (H,), init="bias"),
+                ParamSpec("norm", (H * dv,), init="norm"), ParamSpec("o", (hid, H * dv))]
+
+    def load(self, tensors, rt: Runtime):
+        self.w_in = torch.cat([rt.matrix(tensors[n]) for n in ("q", "k", "v", "g", "i", "f")], dim=0).contiguous()
+        self.i_bias, self.f_bias = rt.vector(tensors["i.b"]), rt.vector(tensors["f.b"])
+        self.norm_w = (rt.vector(tensors["norm"]) * self.out_scale).contiguous()
+        self.w_o = rt.matrix(tensors["o"])
+
+    def state_need(self):
+        return {"memory": RequestState((self.H, self.d, self.dv)), "memory_norm": RequestState((self.H, self.d)),
+                "memory_max": RequestState((self.H, self.dv + 1))}     # equal copies of m: one per column block of the scan
+
+    def forward(self, h, resid, ctx: StepContext, call: int):
+        rt, ops, b = ctx.rt, ctx.rt.ops, ctx.batch
+        H, Hd, Hv = self.H, self.H * self.d, self.H * self.dv
+        proj = ops.linear(h, self.w_in, None, torch.float32)               # [q | k | v | gate | i | f]
+        gates = 2 * Hd + 2 * Hv
+        o, rden = ops.memory_scan(proj[:, :Hd], proj[:, Hd:2 * Hd], proj[:, 2 * Hd:2 * Hd + Hv],
+                                  proj[:, gates:gates + H], proj[:, gates + H:gates + 2 * H], self.i_bias, self.f_bias,
+                                  self.cap, ctx.state(call, "memory"), ctx.state(call, "memory_norm"),
+                                  ctx.state(call, "memory_max"), b, H, self.d, self.dv, q_scale=self.d ** -0.5,
+                                  den_eps=self.den_eps)
+        g = ops.gated_rmsnorm(o, proj[:, 2 * Hd + Hv:gates], self.norm_w, H, self.eps, "sigmoid_after", rt.dtype,
+                              row_scale=rden)
+        ops.linear_add(g, self.w_o, resid)
+
+
 class ParallelMixers(Mixer):
     """Two mixers side by side that read the same input.  ``combine`` ``"norm_mean"``: each output is RMS-normed over
     the model width with a weight of its own (``<name>.out``); the result is ``coef`` times their sum (a half: the
@@ -412,6 +466,7 @@ class ParallelMixers(Mixer):
 register_part("mixer", "gated_delta", GatedDeltaMixer)
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "mamba1", Mamba1Mixer)
+register_part("mixer", "matrix_memory", MatrixMemory)
 register_part("mixer", "retention", RetentionMixer)
 register_part("mixer", "parallel_mixers", ParallelMixers)
 register_part("mixer", "mamba2", Mamba2Mixer)

@@ -1,6 +1,8 @@
 """Position encodings."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..registry import register_part
@@ -36,6 +38,41 @@ class RotaryNeoX(PositionEncoding):
         return self._table, self.rotary_dim
 
 
+def slowed_long_waves(freqs, factor: float, low: float, high: float, original: float):
+    """Frequencies whose long waves are slowed, each in double precision: with wavelength ``L = 2 pi / f``, a wave
+    shorter than ``original / high`` keeps f; one longer than ``original / low`` gets ``f / factor``; between the two,
+    with ``s = (original / L - low) / (high - low)``, it gets ``(1 - s) f / factor + s f``."""
+    out = []
+    for f in freqs:
+        wave = 2.0 * math.pi / f
+        if wave < original / high:
+            out.append(f)
+        elif wave > original / low:
+            out.append(f / factor)
+        else:
+            s = (original / wave - low) / (high - low)
+            out.append((1.0 - s) * f / factor + s * f)
+    return out
+
+
+class RotaryScaledNeoX(RotaryNeoX):
+    """Split-half rotary embedding whose table is ``theta^(-2i / rotary_dim)`` with long waves slowed by
+    ``slowed_long_waves`` (``scaling``: a dict with ``factor``, ``low``, ``high``, ``original``; None: the plain
+    table).  Only the table differs; the kernels index it as any other."""
+
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, scaling: dict | None = None):
+        super().__init__(head_dim, theta, rotary_dim)
+        self.scaling = {k: float(scaling[k]) for k in ("factor", "low", "high", "original")} if scaling else None
+
+    def rotary(self, rt: Runtime):
+        if self._table is None or self._table.device != rt.device:
+            f = [self.theta ** (-2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)]
+            if self.scaling:
+                f = slowed_long_waves(f, **self.scaling)
+            self._table = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(rt.device)
+        return self._table, self.rotary_dim
+
+
 class RotaryInterleaved(RotaryNeoX):
     """The same rotation on neighbouring pairs ``(2i, 2i + 1)`` of every head."""
 
@@ -66,5 +103,6 @@ class LearnedPositions(PositionEncoding):
 
 register_part("position", "learned", LearnedPositions)
 register_part("position", "rope_neox", RotaryNeoX)
+register_part("position", "rope_scaled_neox", RotaryScaledNeoX)
 register_part("position", "rope_interleaved", RotaryInterleaved)
 register_part("position", "none", NoPositionEncoding)

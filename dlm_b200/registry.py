@@ -87,4 +87,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_done = True
     from . import parts  # noqa: F401  registers the built-in parts
-    from .models import qwen2_moe, salolorn, zasazen, zesapel  # noqa: F401  register the architectures
+    from .models import faguzen, qwen2_moe, salolorn, zasazen, zesapel  # noqa: F401  register the architectures

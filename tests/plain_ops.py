@@ -94,8 +94,10 @@ class PlainOps:
             v = x / (1.0 + torch.exp(-x))
         return v.to(out_dtype)
 
-    def gated_rmsnorm(self, y, gate, w, groups, eps, mode, out_dtype):
+    def gated_rmsnorm(self, y, gate, w, groups, eps, mode, out_dtype, row_scale=None):
         T, C = y.shape
+        if row_scale is not None:          # a factor per token and group, before anything else
+            y = (y.reshape(T, groups, C // groups) * row_scale[:, :, None]).reshape(T, C)
         v = y * (gate / (1.0 + torch.exp(-gate))) if mode == "silu_before" else y
         v = v.reshape(T, groups, C // groups)
         v = (v * (1.0 / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))).reshape(T, C)
@@ -448,7 +450,7 @@ class PlainOps:
         return q.reshape(T, Q).to(out_dtype)
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len, num_single=0, slopes=None, chunk=0, sinks=None):
+                  max_kv_len, num_single=0, slopes=None, chunk=0, sinks=None, softcap=0.0):
         T = q.shape[0]
         ps = k_cache.shape[2]
         out = torch.zeros((T, nh * hd), dtype=torch.float32, device=q.device)
@@ -476,6 +478,8 @@ class PlainOps:
                 ok &= torch.div(pos, chunk, rounding_mode="floor")[None, :] == torch.div(qpos, chunk, rounding_mode="floor")[:, None]
             for h in range(nh):
                 s = (qs[:, h, :] @ k[:, h // group, :].T) * scale
+                if softcap > 0:
+                    s = softcap * torch.tanh(s / softcap)
                 if slopes is not None:
                     s = s - slopes[h] * (qpos[:, None] - pos[None, :]).to(torch.float32)
                 s = s.masked_fill(~ok, float("-inf"))
@@ -484,6 +488,46 @@ class PlainOps:
                 p = torch.softmax(s, dim=-1)[:, :pos.numel()]
                 out[cu[r]:cu[r + 1], h * hd:(h + 1) * hd] = p @ v[:, h // group, :]
         return out.to(q.dtype)
+
+    def dyt_norm(self, x, w, b, alpha, out_dtype, rows=None):
+        if rows is not None:
+            x = x[rows.long()]
+        return (torch.tanh(alpha * x) * w + b).to(out_dtype)
+
+    def tanh_cap(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
+
+    def entry_gate(self, o, gate, nh, dv, D, factor=1.0):
+        T = o.shape[0]
+        v = _f(o).reshape(T, nh, D).clone()
+        v[:, :, :dv] = v[:, :, :dv] * (factor * torch.sigmoid(gate.reshape(T, nh, dv)))
+        o.copy_(v.reshape(T, nh * D).to(o.dtype))
+
+    def memory_scan(self, q, k, v, igate, fgate, i_bias, f_bias, cap, S, n, m, batch, heads, dk, dv, q_scale=1.0,
+                    den_eps=1e-6):
+        T = v.shape[0]
+        q_ = q.reshape(T, heads, dk) * q_scale
+        k_ = k.reshape(T, heads, dk)
+        v_ = v.reshape(T, heads, dv)
+        li = cap * torch.tanh((igate + i_bias) / cap)
+        lf = torch.nn.functional.logsigmoid(cap * torch.tanh((fgate + f_bias) / cap))
+        out = torch.zeros((T, heads * dv), dtype=torch.float32, device=v.device)
+        rden = torch.zeros((T, heads), dtype=torch.float32, device=v.device)
+        cu, slots = batch.cu_q.tolist(), batch.state_slot.tolist()
+        for r in range(batch.num_requests):
+            Sr, nr, mall = S[slots[r]], n[slots[r]], m[slots[r]]       # [heads, dk, dv], [heads, dk], [heads, dv + 1]
+            mr = mall[:, 0].clone()                                    # the copies of m are equal
+            for t in range(cu[r], cu[r + 1]):
+                new = torch.maximum(lf[t] + mr, li[t])
+                keep, put = torch.exp(lf[t] + mr - new), torch.exp(li[t] - new)
+                kp = put[:, None] * k_[t]
+                Sr.copy_(keep[:, None, None] * Sr + kp[:, :, None] * v_[t][:, None, :])
+                nr.copy_(keep[:, None] * nr + kp)
+                mr = new
+                mall.copy_(new[:, None].expand_as(mall))
+                out[t] = torch.einsum("hij,hi->hj", Sr, q_[t]).reshape(heads * dv)
+                rden[t] = 1.0 / (torch.maximum((nr * q_[t]).sum(-1).abs(), torch.exp(-new)) + den_eps)
+        return out, rden
 
     # ------------------------------------------------------------------- moe
     def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
@@ -503,7 +547,7 @@ class PlainOps:
         wts = torch.gather(probs, 1, ids)
         if norm:
             s = wts.sum(-1, keepdim=True)
-            wts = torch.where(s > 0, wts / s, wts)
+            wts = torch.where(s > 0, wts / (s + 1e-20 if norm == 2 else s), wts)
         return ids.to(torch.int32), wts * scale, gate
 
     def route(self, h, w, E, k, norm, has_gate, input_settled=False, **kw):
@@ -522,14 +566,21 @@ class PlainOps:
         dest[order] = torch.arange(T * k, dtype=torch.int32, device=ids.device)
         return offsets, rows, dest.reshape(T, k)
 
-    def moe_combine(self, y, dest, wts, shared, gate, resid):
+    def moe_combine(self, y, dest, wts, shared, gate, resid, ids=None, num_real=0, passthrough=None, shared_scale=1.0):
         T, k = dest.shape
         acc = torch.zeros_like(resid)
         for j in range(k):
-            acc = acc + wts[:, j:j + 1] * y[dest[:, j].long()]
+            if ids is None:
+                src = y[dest[:, j].long()]
+            else:                               # experts from num_real on hand the token's own row through
+                real = ids[:, j] < num_real
+                src = passthrough.clone()
+                if y is not None and bool(real.any()):
+                    src[real] = y[dest[real, j].long()]
+            acc = acc + wts[:, j:j + 1] * src
         if shared is not None:
             g = gate[:, None] if gate is not None else 1.0
-            acc = acc + g * shared
+            acc = acc + (g * shared_scale) * shared
         resid += acc
 
     # -------------------------------------------------------------- sampling
