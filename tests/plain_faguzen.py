@@ -153,16 +153,21 @@ def route(h, p, mlp):
     too); the choice looks at score + correction, the weights at the scores alone, divided by their sum."""
     top = mlp["router"]["top"]
     s = torch.softmax(h @ p("router").T, dim=-1)
-    ids = torch.topk(s + p("correction"), top, dim=-1).indices
+    pick = torch.sort(s + p("correction"), dim=-1, descending=True, stable=True)
+    ids = pick.indices[:, :top]
     w = torch.gather(s, 1, ids)
-    return ids, w / (w.sum(-1, keepdim=True) + 1e-20), s
+    # how clear the choice was: the last chosen expert's lead over the first one left out
+    gap = pick.values[:, top - 1] - pick.values[:, top] if top < s.shape[1] else torch.full_like(s[:, 0], math.inf)
+    return ids, w / (w.sum(-1, keepdim=True) + 1e-20), gap
 
 
-def expert_mixture(h, p, mlp, rounded=False):
+def expert_mixture(h, p, mlp, rounded=False, gaps=None):
     """Routed two-matrix experts, of which the last ``identity`` hand their input through, plus a shared expert."""
     E, ident = mlp["router"]["experts"], mlp["router"].get("identity", 0)
     hh = as_stored(h, rounded)
-    ids, w, _ = route(h, p, mlp)
+    ids, w, gap = route(h, p, mlp)
+    if gaps is not None:
+        gaps.append(gap)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(ids[t].tolist(), w[t]):
@@ -190,11 +195,13 @@ def layer_runs(cfg):
 
 class PlainFaguzen:
     """``tensors``: name -> tensor as stored.  ``forward(tokens)`` gives logits at every position and, with
-    ``trace=True``, also the residual after every layer run."""
+    ``trace=True``, also the residual after every layer run; ``last_gaps`` then holds, per position, how clear the
+    least clear choice of experts was."""
 
     def __init__(self, config: dict, tensors: dict, dtype=torch.float64, rounded=False):
         self.cfg, self.dtype, self.rounded = config, dtype, rounded
         self.t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
+        self._gaps, self.last_gaps = [], None
 
     def norm(self, name, x):
         t = self.t
@@ -208,18 +215,23 @@ class PlainFaguzen:
                            cfg["norm"]["eps"], self.rounded)
         if spec.get("mlp") is not None:
             assert spec["mlp"]["kind"] == "moe"
-            y = y + expert_mixture(self.norm(f"l{i}.norm2", x), lambda n: t[f"l{i}.mlp.{n}"], spec["mlp"], self.rounded)
+            y = y + expert_mixture(self.norm(f"l{i}.norm2", x), lambda n: t[f"l{i}.mlp.{n}"], spec["mlp"], self.rounded,
+                                   self._gaps)
         return x + cfg.get("residual_mult", 1.0) * y
 
     def forward(self, tokens, trace=False):
         cfg, t = self.cfg, self.t
         x = t["embed"][torch.as_tensor(tokens, dtype=torch.long)].clone()
         after = []
+        self._gaps = []
         for i, opens in layer_runs(cfg):
             if opens is not None:
                 x = x + t["loop.step"][opens]
             x = self.layer(i, x)
             after.append(x)
+        # per position, the least clear choice of experts over all layer runs
+        self.last_gaps = torch.stack(self._gaps).min(0).values if self._gaps else torch.full((x.shape[0],), math.inf,
+                                                                                              dtype=self.dtype)
         y = as_stored(self.norm("final.norm", x), self.rounded)
         logits = tanh_cap(y @ t["head"].T, cfg.get("logit_softcap"))
         return (logits, torch.stack(after)) if trace else logits
