@@ -170,7 +170,7 @@ GAP = {"float32": 2e-5, "bfloat16": 5e-3}
 CARRY = {"float32": 0, "bfloat16": 6}
 
 
-def references(oracle, reqs, dtype):
+def references(oracle, reqs, dtype, gap=None, carry=None):
     """Per request the exact logits, a limit for every position, and which positions are compared.  The limit is TOL,
     or in bfloat16 three times the error that rounding alone causes (the plain model with bfloat16 where an engine
     must round) where that is more; the error that rounding causes at a position is taken as the larger of the
@@ -180,9 +180,9 @@ def references(oracle, reqs, dtype):
     for rid, t in reqs.items():
         ref[rid] = oracle.forward(t)
         gaps = oracle.last_gaps
-        clear = gaps >= GAP[dtype]
+        clear = gaps >= (GAP[dtype] if gap is None else gap)
         for at in (~clear).nonzero().flatten().tolist():
-            clear[at:at + 1 + CARRY[dtype]] = False
+            clear[at:at + 1 + (CARRY[dtype] if carry is None else carry)] = False
         ok[rid] = clear
         lim[rid] = torch.full((len(t),), TOL[dtype], dtype=torch.float64)
     if dtype == "bfloat16":
@@ -209,3 +209,11 @@ def within_limits(got, ref, lim, ok):
     beyond one and a half times its limit and at most one in fifty is beyond it."""
     r = ratios(got, ref, lim, ok)
     return max(r, default=0.0) < 1.5 and sum(x > 1.0 for x in r) <= len(r) // 50
+
+
+def mostly_within_limits(got, ref, lim, ok):
+    """For a model wide enough that rounding now and then turns a choice of experts which the lead did not mark as
+    close: such a turn shows at a few positions behind it and nowhere else, a fault of a kernel shows everywhere.  At
+    most one row in fifty is beyond its limit, and the median row is within half of it."""
+    r = sorted(ratios(got, ref, lim, ok))
+    return sum(x > 1.0 for x in r) <= len(r) // 50 and r[len(r) // 2] < 0.5
