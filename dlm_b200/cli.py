@@ -72,8 +72,8 @@ def build_parser() -> argparse.ArgumentParser:
 def demo_config(args) -> dict:
     """The config.json of the demo model the geometry options describe (the reference's demo is a
     dense model, src/main.rs:404-470; here it has experts too, since that is what this engine is for)."""
-    from .registry import architectures
-    return dict(architectures=[architectures()[0]], vocab_size=args.vocab_size, hidden_size=args.hidden_size,
+    from .config import Qwen2MoeConfig          # the geometry options are that architecture's keys
+    return dict(architectures=[Qwen2MoeConfig.architecture], vocab_size=args.vocab_size, hidden_size=args.hidden_size,
                 num_hidden_layers=args.num_layers, num_attention_heads=args.num_heads,
                 num_key_value_heads=args.num_kv_heads, intermediate_size=args.intermediate_size,
                 num_experts=args.num_experts, num_experts_per_tok=args.num_experts_per_tok,
