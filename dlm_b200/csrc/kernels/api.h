@@ -329,8 +329,9 @@ void dyt_norm_pair(const float* x, const float* wa, const float* ba, float alpha
                    cudaStream_t stream);
 // x[i] = cap * tanh(x[i] / cap) for n floats, in place
 void tanh_cap(float* x, long long n, float cap, cudaStream_t stream);
-// o[t, h * D + i] *= factor * sigmoid(gate[t * ldg + h * dv + i]) for i < dv, in place (o in `dtype`, gate f32 raw)
+// o[t, h * D + i] *= factor * sigmoid(gate[t * ldg + h * dv + i]) for i < dv, in place (o in `dtype`, gate f32 raw);
+// resid (f32 [T, W]) != nullptr: also resid[t, :] += bias[:]
 void entry_gate(void* o, const float* gate, int ldg, int T, int nh, int dv, int D, float factor, int dtype,
-                cudaStream_t stream);
+                float* resid, const float* bias, int W, cudaStream_t stream);
 
 }  // namespace dlmk

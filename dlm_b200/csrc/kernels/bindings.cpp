@@ -264,8 +264,10 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                             T, H, out_dtype, st(stream));
     });
     m.def("tanh_cap", [](u64 x, long long n, float cap, u64 stream) { dlmk::tanh_cap(ptr<float>(x), n, cap, st(stream)); });
-    m.def("entry_gate", [](u64 o, u64 gate, int ldg, int T, int nh, int dv, int D, float factor, int dtype, u64 stream) {
-        dlmk::entry_gate(ptr<void>(o), ptr<const float>(gate), ldg, T, nh, dv, D, factor, dtype, st(stream));
+    m.def("entry_gate", [](u64 o, u64 gate, int ldg, int T, int nh, int dv, int D, float factor, int dtype, u64 resid,
+                           u64 bias, int W, u64 stream) {
+        dlmk::entry_gate(ptr<void>(o), ptr<const float>(gate), ldg, T, nh, dv, D, factor, dtype, ptr<float>(resid),
+                         ptr<const float>(bias), W, st(stream));
     });
     m.def("take_error_flag", &dlmk::take_error_flag);
     m.def("reset_decode_merge_counters", [](u64 stream) { dlmk::reset_decode_merge_counters(st(stream)); });

@@ -52,12 +52,16 @@ __global__ void tanh_cap_kernel(float* x, long long n, float cap, float inv_cap)
 }
 
 // o[t, h * D + i] *= factor * sigmoid(gate[t * ldg + h * dv + i]) for i < dv, in place (entries from dv on are the
-// padding of a head stored wider than its values and stay as they are)
+// padding of a head stored wider than its values and stay as they are); with resid != nullptr also
+// resid[t, :] += bias[:] (W entries): the bias of the projection that follows, added by the launch that is there anyway
 template <typename T>
-__global__ void entry_gate_kernel(T* o, const float* gate, int ldg, int nh, int dv, int D, float factor) {
+__global__ void entry_gate_kernel(T* o, const float* gate, int ldg, int nh, int dv, int D, float factor, float* resid,
+                                  const float* __restrict__ bias, int W) {
     dep_wait();
     dep_launch_next();
     const int t = blockIdx.x;
+    if (resid != nullptr)                                  // the output projection's bias joins the token's residual row
+        for (int i = threadIdx.x; i < W; i += blockDim.x) resid[(long long)t * W + i] += bias[i];
     T* row = o + (long long)t * nh * D;
     const float* g = gate + (long long)t * ldg;
     constexpr int U = 4;
@@ -120,14 +124,16 @@ void tanh_cap(float* x, long long n, float cap, cudaStream_t stream) {
 }
 
 void entry_gate(void* o, const float* gate, int ldg, int T, int nh, int dv, int D, float factor, int dtype,
-                cudaStream_t stream) {
+                float* resid, const float* bias, int W, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(D >= dv && dv >= 1, "entry_gate: the stored head size must hold the values");
+    DLM_CHECK(resid == nullptr || (bias != nullptr && W > 0), "entry_gate: a residual to add to needs the bias and its width");
     if (dtype == F32)
-        launch_dep(entry_gate_kernel<float>, dim3(T), dim3(256), 0, stream, static_cast<float*>(o), gate, ldg, nh, dv, D, factor);
+        launch_dep(entry_gate_kernel<float>, dim3(T), dim3(256), 0, stream, static_cast<float*>(o), gate, ldg, nh, dv, D,
+                   factor, resid, bias, W);
     else
         launch_dep(entry_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, static_cast<__nv_bfloat16*>(o), gate,
-                   ldg, nh, dv, D, factor);
+                   ldg, nh, dv, D, factor, resid, bias, W);
     check_launch("entry_gate");
 }
 

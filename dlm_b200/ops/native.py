@@ -423,14 +423,21 @@ class NativeOps:
         self.launches += 1
         self.k.tanh_cap(_p(x), x.numel(), float(cap), self._stream())
 
-    def entry_gate(self, o, gate, nh, dv, D, factor=1.0):
+    def entry_gate(self, o, gate, nh, dv, D, factor=1.0, resid=None, bias=None):
         """``o[t, h * D + i] *= factor * sigmoid(gate[t, h * dv + i])`` for ``i < dv``, in place (``gate`` 32-bit,
-        may be a column slice; heads stored ``D`` wide keep their padding)."""
+        may be a column slice; heads stored ``D`` wide keep their padding).  With ``resid`` (32-bit ``[T, W]``) and
+        ``bias`` (``[W]``) the same launch also does ``resid[t] += bias``."""
         T = o.shape[0]
         assert o.shape[1] == nh * D and o.is_contiguous() and gate.dtype == torch.float32
         assert gate.shape == (T, nh * dv) and gate.stride(1) == 1
+        W = 0
+        if resid is not None:
+            W = resid.shape[1]
+            assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[0] == T
+            assert bias is not None and bias.shape == (W,) and bias.dtype == torch.float32 and bias.is_contiguous()
         self.launches += 1
-        self.k.entry_gate(_p(o), _p(gate), gate.stride(0), T, nh, dv, D, float(factor), _dt(o.dtype), self._stream())
+        self.k.entry_gate(_p(o), _p(gate), gate.stride(0), T, nh, dv, D, float(factor), _dt(o.dtype), _p(resid),
+                          _p(bias if resid is not None else None), W, self._stream())
 
     def memory_scan(self, q, k, v, igate, fgate, i_bias, f_bias, cap, S, n, m, batch, heads, dk, dv, q_scale=1.0,
                     den_eps=1e-6):

@@ -368,15 +368,18 @@ class HeadNormedAttention(Mixer):
         o = ops.attention(q, view.k, view.v, view.group.block_table, b.cu_q, b.kv_len, self.window or 0, self.scale,
                           H, G, self.D, b.max_q_len, b.max_kv_len, b.num_single, chunk=self.chunk or 0, sinks=self.sink,
                           **extra)
+        bias = self.b_o                                # the output bias still to be added (None: none, or done)
         if self.has_gate:
             g = proj[:, (H + G) * d + G * dv:]
             if self.gate_rows == H:
                 ops.head_gate(o, g, H, self.D, self.out_scale)
             else:
-                ops.entry_gate(o, g, H, dv, self.D, self.out_scale)
+                # the output bias rides along: the same launch adds it to the token's residual row
+                ops.entry_gate(o, g, H, dv, self.D, self.out_scale, resid=resid if bias is not None else None, bias=bias)
+                bias = None
         ops.linear_add(o, self.w_o, resid)
-        if self.b_o is not None:
-            ops.add_vec_rows(resid, None, self.b_o)
+        if bias is not None:
+            ops.add_vec_rows(resid, None, bias)
 
 
 register_part("mixer", "gqa_attention", GroupedQueryAttention)

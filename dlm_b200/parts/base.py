@@ -129,6 +129,12 @@ class Norm(Part):
         ``out_dtype``, the runtime's activation dtype when None."""
         raise NotImplementedError
 
+    def pair_with(self, other: "Norm"):
+        """None, or a function ``(x_f32, rt, want_f32) -> (a, b, b32)`` that applies this norm and ``other`` to the
+        same rows in one pass: a and b in the activation dtype, b once more in 32-bit when ``want_f32`` (else None).
+        A block whose two sublayers read the same rows asks for it."""
+        return None
+
     def fusable_rms(self) -> tuple[torch.Tensor, float] | None:
         """``(weight, eps)`` if this norm is a plain RMS norm that a kernel may apply itself to the
         32-bit residual (the router's kernel does), else None: the caller then asks ``forward`` for a
@@ -163,6 +169,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    # True for a part whose ``forward`` takes ``normed32``: its normalised input once more in 32-bit, when the block
+    # has it at hand (it then need not apply ``pre_norm`` again itself)
+    takes_normed32 = False
 
     def forward(self, h: torch.Tensor, resid: torch.Tensor, ctx: "StepContext", pre_norm: "Norm | None" = None) -> None:
         """``pre_norm`` is the norm that produced ``h`` from ``resid``; a part that needs the

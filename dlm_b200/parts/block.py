@@ -78,12 +78,20 @@ class ParallelBlock(PreNormBlock):
             self.mixer.forward(self.norm1.forward(resid, rt), resid, ctx, call)
             return
         a, b = self.norm1.fusable_rms(), self.norm2.fusable_rms()
+        both = self.norm1.pair_with(self.norm2)
+        extra = {}
         if a is not None and b is not None and a[1] == b[1]:
             # two RMS norms of the same rows: one statistic, one pass
             h1, h2 = rt.ops.rmsnorm_pair(resid, a[0], b[0], a[1], rt.dtype)
+        elif both is not None:
+            # two norms that can share a pass over the rows; a feed-forward that wants its input in 32-bit as well
+            # (a router) gets it from the same pass
+            h1, h2, h32 = both(resid, rt, self.ffn.takes_normed32)
+            if self.ffn.takes_normed32:
+                extra["normed32"] = h32
         else:
             h1, h2 = self.norm1.forward(resid, rt), self.norm2.forward(resid, rt)
-        self.ffn.forward(h2, resid, ctx, pre_norm=self.norm2)
+        self.ffn.forward(h2, resid, ctx, pre_norm=self.norm2, **extra)
         self.mixer.forward(h1, resid, ctx, call)
 
 

@@ -215,7 +215,9 @@ class RoutedActExperts(FeedForward):
         if self.Is:
             self.ws_up, self.ws_down = rt.matrix(tensors["shared.up"]), rt.matrix(tensors["shared.down"])
 
-    def forward(self, h, resid, ctx: StepContext, pre_norm=None):
+    takes_normed32 = True
+
+    def forward(self, h, resid, ctx: StepContext, pre_norm=None, normed32=None):
         ops = ctx.rt.ops
         shared = None
         branch = ops.branch(h.shape[0])
@@ -226,7 +228,9 @@ class RoutedActExperts(FeedForward):
                 shared = ops.linear(sact, self.ws_down, None, torch.float32)
         # the router (and the identity experts) read the normalised residual in 32-bit
         rms = pre_norm.fusable_rms() if pre_norm is not None else None
-        if rms is not None:
+        if normed32 is not None:
+            x = normed32
+        elif rms is not None:
             x = ops.rmsnorm(resid, rms[0], rms[1], torch.float32)
         elif pre_norm is not None:
             x = pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)

@@ -54,6 +54,15 @@ class DynamicTanh(Norm):
     def forward(self, x, rt: Runtime, rows=None, out_dtype=None):
         return rt.ops.dyt_norm(x, self.weight, self.bias, self.alpha, out_dtype or rt.dtype, rows)
 
+    def pair_with(self, other):
+        if not isinstance(other, DynamicTanh) or other.size != self.size:
+            return None
+
+        def both(x, rt: Runtime, want_f32: bool):
+            return rt.ops.dyt_norm_pair(x, self.weight, self.bias, self.alpha, other.weight, other.bias, other.alpha,
+                                        rt.dtype, want_f32=want_f32)
+        return both
+
 
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "dynamic_tanh", DynamicTanh)

@@ -494,11 +494,17 @@ class PlainOps:
             x = x[rows.long()]
         return (torch.tanh(alpha * x) * w + b).to(out_dtype)
 
+    def dyt_norm_pair(self, x, wa, ba, alpha_a, wb, bb, alpha_b, out_dtype, want_f32=False):
+        b32 = torch.tanh(alpha_b * x) * wb + bb
+        return (torch.tanh(alpha_a * x) * wa + ba).to(out_dtype), b32.to(out_dtype), (b32 if want_f32 else None)
+
     def tanh_cap(self, x, cap):
         x.copy_(cap * torch.tanh(x / cap))
 
-    def entry_gate(self, o, gate, nh, dv, D, factor=1.0):
+    def entry_gate(self, o, gate, nh, dv, D, factor=1.0, resid=None, bias=None):
         T = o.shape[0]
+        if resid is not None:
+            resid += bias
         v = _f(o).reshape(T, nh, D).clone()
         v[:, :, :dv] = v[:, :, :dv] * (factor * torch.sigmoid(gate.reshape(T, nh, dv)))
         o.copy_(v.reshape(T, nh * D).to(o.dtype))

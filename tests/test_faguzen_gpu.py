@@ -108,6 +108,11 @@ def test_cap_on_logits_and_gate_per_entry(ops, dtype):
         assert torch.allclose(o.float().cpu(), want.float(), atol=1e-6 if dtype == torch.float32 else 2e-2, rtol=1e-2)
         pad = o.reshape(T, nh, D)[:, :, dv:]
         assert torch.equal(pad, before.reshape(T, nh, D)[:, :, dv:])     # the heads' padding is not touched
+        # the same launch may add a bias to every token's row of the residual
+        o2, resid, bias = before.clone(), randn(T, 70, seed=4), randn(70, seed=5)
+        want_resid = resid.cpu() + bias.cpu()
+        ops.entry_gate(o2, gate, nh, dv, D, 0.7, resid=resid, bias=bias)
+        assert torch.equal(o2, o) and torch.allclose(resid.cpu(), want_resid, atol=1e-6)
     ops.check_errors()
 
 
