@@ -12,6 +12,7 @@ continuous-batching workload on the windowed variant of the model (`serving`).
     python bench.py --workload zesapel      # the Zesapel design beside Qwen2-MoE at equal sizes, and its kernels alone
     python bench.py --workload zasazen      # the Zasazen design beside Qwen2-MoE at equal sizes, and its kernels alone
     python bench.py --workload salolorn     # the Salolorn design beside a dense Qwen2 at equal sizes, and its kernels alone
+    python bench.py --workload faguzen      # the Faguzen design beside Qwen2-MoE at equal sizes, and its kernels alone
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -1113,6 +1114,202 @@ def run_salolorn(args, pk) -> dict:
     return out
 
 
+def faguzen_config(width, vocab=32768):
+    """Four layers of the design at a real model's layer sizes, the middle two run twice (6 layer runs): attention
+    heads of 128 (four query heads a key/value head, half of each head rotated), a matrix memory with heads of 64 x 128,
+    16 experts of `width / 2` of which each token takes 2 out of 16 + 2 (two identity experts), a shared expert of
+    `width`; the last layer has no feed-forward."""
+    heads = width // 128
+    mixer = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                      "softcap": 30.0, "rot": {"base": 1e4, "dims": 64,
+                                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}},
+             "right": {"heads": width // 128, "dim": 64, "vdim": 128, "gate_cap": 12.0}, "left_scale": 1.0, "right_scale": 1.0}
+    mlp = {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 2}, "expert": {"ff": width // 2},
+           "shared": {"ff": width}}
+    layers = [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(3)] + [{"type": "parallel", "mixer": mixer, "mlp": None}]
+    return {"architecture": "Faguzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "logit_softcap": 30.0, "max_positions": 8192, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
+
+
+def qwen_config_like_faguzen(z):
+    """Qwen2-MoE with the same width and vocabulary and as many layers as the design has layer runs; attention heads
+    of the same number and size; the same experts (count, size, two a token) and shared expert in every layer."""
+    from dlm_b200.models.zasazen import layer_order
+    runs = len(layer_order(len(z["layers"]), z.get("loop")))
+    left, mlp = z["layers"][0]["mixer"]["left"], z["layers"][0]["mlp"]
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=runs, hidden_size=z["width"],
+                num_attention_heads=left["heads"], num_key_value_heads=left["kv_heads"], head_dim=left["dim"],
+                num_experts=mlp["router"]["experts"], num_experts_per_tok=mlp["router"]["top"],
+                moe_intermediate_size=mlp["expert"]["ff"], shared_expert_intermediate_size=mlp["shared"]["ff"],
+                norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], intermediate_size=z["width"],
+                vocab_size=z["vocab"], rope_theta=10000.0, rms_norm_eps=1e-6, use_sliding_window=False,
+                tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def faguzen_kernels(z, pk, batch, context, prefill_tokens):
+    """Each kernel of the design alone at the layer sizes of `z`, beside the like kernel of an existing model at the
+    same sizes: a prompt of `prefill_tokens` tokens of one request, and a decode step of `batch` requests at `context`
+    tokens.  Microseconds (median of 5, the cache flushed before each), the bytes the kernel has to move at least,
+    and that over time over the measured copy bandwidth; the attentions also with their flops."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from dlm_b200.ops import native_ops
+    ops = native_ops(fast=True)
+    dev = "cuda"
+    W = z["width"]
+    mixer, mlp = z["layers"][0]["mixer"], z["layers"][0]["mlp"]
+    lf, rt = mixer["left"], mixer["right"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    bf = torch.bfloat16
+    rows = {}
+
+    def timed(name, case, fn, nbytes, flop=None):
+        ts = []
+        for _ in range(6):
+            _flush(torch, flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        us = statistics.median(ts[1:]) * 1e3
+        row = {"us": round(us, 1), "mbytes": round(nbytes / 1e6, 2),
+               "frac_of_copy": round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)}
+        if flop is not None:
+            row["gflop"] = round(flop / 1e9, 2)
+            row["frac_of_bf16_peak"] = round(flop / (us * 1e-6) / (pk["bf16_tflops"] * 1e12), 4)
+        rows.setdefault(name, {})[case] = row
+
+    for case, lens, start in (("prefill", [prefill_tokens], 0), ("decode", [1] * batch, context)):
+        T, R = sum(lens), len(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        b = SimpleNamespace(num_requests=R, cu_q=torch.tensor(cu, **i32), state_slot=torch.arange(R, **i32),
+                            token_req=torch.tensor([r for r, n in enumerate(lens) for _ in range(n)], **i32),
+                            positions=torch.tensor([start + i for n in lens for i in range(n)], **i32))
+        held = start + max(lens)
+        pages_each = -(-held // 64)
+        table = torch.arange(R * pages_each, **i32).reshape(R, pages_each)
+        slots = torch.cat([table[r, (start + torch.arange(n, device=dev)) // 64] * 64 + (start + torch.arange(n, device=dev)) % 64
+                           for r, n in enumerate(lens)]).to(torch.int32)
+        kv_len = torch.tensor([start + n for n in lens], **i32)
+        single = sum(1 for n in lens if n == 1)
+        # ---- the norm without statistics beside the RMS norm, alone and in pairs
+        resid = torch.randn(T, W, device=dev)
+        wv, bv = torch.randn(W, device=dev), torch.randn(W, device=dev)
+        timed("dyt_norm", case, lambda: ops.dyt_norm(resid, wv, bv, 0.7, bf), T * W * 6)
+        timed("rmsnorm (Qwen2's)", case, lambda: ops.rmsnorm(resid, wv, 1e-6, bf), T * W * 6)
+        timed("dyt_norm_pair (two norms and the router's 32-bit input)", case,
+              lambda: ops.dyt_norm_pair(resid, wv, bv, 0.7, wv, bv, 0.9, bf, want_f32=True), T * W * 12)
+        timed("rmsnorm_pair (Zasazen's)", case, lambda: ops.rmsnorm_pair(resid, wv, wv, 1e-6, bf), T * W * 8)
+        # ---- matrix memory with a running maximum, beside the recurrences with one decay per head
+        H2, d2, dv2 = rt["heads"], rt["dim"], rt["vdim"]
+        mp = torch.randn(T, 2 * H2 * d2 + 2 * H2 * dv2 + 2 * H2, device=dev)
+        q_, k_, v_ = mp[:, :H2 * d2], mp[:, H2 * d2:2 * H2 * d2], mp[:, 2 * H2 * d2:2 * H2 * d2 + H2 * dv2]
+        g_ = mp[:, 2 * H2 * d2 + H2 * dv2:2 * H2 * d2 + 2 * H2 * dv2]
+        ig, fg = mp[:, -2 * H2:-H2], mp[:, -H2:]
+        ib, fb = torch.zeros(H2, device=dev), torch.ones(H2, device=dev)
+        S, nst, mst = (torch.zeros(R + 1, H2, d2, dv2, device=dev), torch.zeros(R + 1, H2, d2, device=dev),
+                       torch.zeros(R + 1, H2, dv2 + 1, device=dev))
+        scan_bytes = T * (2 * H2 * d2 + 2 * H2 * dv2 + 2 * H2) * 4 + 2 * R * H2 * d2 * dv2 * 4
+        timed("memory_scan (exponential gates, running maximum, normaliser)", case,
+              lambda: ops.memory_scan(q_, k_, v_, ig, fg, ib, fb, rt["gate_cap"], S, nst, mst, b, H2, d2, dv2,
+                                      q_scale=d2 ** -0.5), scan_bytes + T * H2 * 4)
+        A_log, dtb = torch.rand(H2, device=dev) - 1.0, torch.randn(H2, device=dev)
+        gst = torch.zeros(R + 1, H2, d2, dv2, device=dev)
+        timed("gated_scan, delta rule with a decay per head (Salolorn's)", case,
+              lambda: ops.gated_scan(q_, k_, v_, fg, ig, gst, b, H2, H2, d2, dv2, unit_eps=1e-6, q_scale=d2 ** -0.5,
+                                     A_log=A_log, decay_bias=dtb), scan_bytes)
+        rp = torch.randn(T, H2 * dv2 + 2 * H2 * d2, device=dev)
+        decay = torch.tensor([1.0 - 2.0 ** (-5 - 5 * i / max(H2 - 1, 1)) for i in range(H2)], device=dev)
+        timed("ssm_scan with constant decays (Zasazen's retention)", case,
+              lambda: ops.ssm_scan(rp, None, None, None, None, gst, b, H2, dv2, d2, H2, fixed_decay=decay),
+              T * (H2 * dv2 * 2 + 2 * H2 * d2) * 4 + 2 * R * H2 * d2 * dv2 * 4)
+        o_, rden = ops.memory_scan(q_, k_, v_, ig, fg, ib, fb, rt["gate_cap"], S, nst, mst, b, H2, d2, dv2, q_scale=d2 ** -0.5)
+        nw = torch.randn(H2 * dv2, device=dev)
+        timed("gated_rmsnorm (per head, a factor per row, sigmoid gate)", case,
+              lambda: ops.gated_rmsnorm(o_, g_, nw, H2, 1e-6, "sigmoid_after", bf, row_scale=rden), T * H2 * dv2 * 10)
+        timed("gated_rmsnorm (per head, silu gate; Salolorn's)", case,
+              lambda: ops.gated_rmsnorm(o_, g_, nw, H2, 1e-6, "silu_after", bf), T * H2 * dv2 * 10)
+        # ---- attention with capped scores and a gate per entry, beside the plain causal attention
+        Ha, Ga, da, dva = lf["heads"], lf["kv_heads"], lf["dim"], lf["vdim"]
+        D = max(da, dva)
+        k_cache = (torch.randn(R * pages_each + 1, Ga, 64, D, device=dev) * 0.3).to(bf)
+        v_cache = (torch.randn(R * pages_each + 1, Ga, 64, D, device=dev) * 0.3).to(bf)
+        aq = torch.randn(T, (Ha + Ga) * da + Ga * dva + Ha * dva, device=dev)
+        rd = lf["rot"]["dims"]
+        freq = torch.tensor([1e4 ** (-2.0 * i / rd) for i in range(rd // 2)], device=dev)
+        io = T * ((Ha + Ga) * da + Ga * dva) * 4 + T * (Ha + 2 * Ga) * D * 2
+        timed("head_norm_rope_write (no norms, half of each head rotated)", case,
+              lambda: ops.head_norm_rope_write(aq, b.positions, None, None, 1e-6, freq, rd, False, slots, k_cache, v_cache,
+                                               Ha, Ga, da, dva, D, bf), io)
+        pq = torch.randn(T, (Ha + 2 * Ga) * D, device=dev)
+        ffreq = torch.tensor([1e4 ** (-2.0 * i / D) for i in range(D // 2)], device=dev)
+        timed("rope_kv_write (Qwen2's)", case,
+              lambda: ops.rope_kv_write(pq, b.positions, ffreq, D, slots, k_cache, v_cache, Ha, Ga, D, bf), io)
+        q = ops.head_norm_rope_write(aq, b.positions, None, None, 1e-6, freq, rd, False, slots, k_cache, v_cache, Ha, Ga,
+                                     da, dva, D, bf)
+        keys = sum(start + i + 1 for n in lens for i in range(n))
+        nbytes = (R if case == "decode" else 1) * held * Ga * D * 4 + T * Ha * D * 4
+        for name, cap in (("attention, causal, scores capped", lf["softcap"]), ("attention, causal (Qwen2's)", 0.0)):
+            timed(name, case, lambda: ops.attention(q, k_cache, v_cache, table, b.cu_q, kv_len, 0, lf["scale"], Ha, Ga, D,
+                                                    max(lens), held, single, softcap=cap), nbytes, flop=4.0 * keys * Ha * D)
+        o2 = torch.randn(T, Ha * D, device=dev).to(bf)
+        gate = aq[:, (Ha + Ga) * da + Ga * dva:]
+        timed("entry_gate (with the output bias)", case,
+              lambda: ops.entry_gate(o2, gate, Ha, dva, D, 1.0, resid=resid, bias=wv), T * Ha * D * 8 + T * W * 8)
+        timed("head_gate (Salolorn's)", case, lambda: ops.head_gate(o2, gate[:, :Ha], Ha, D, 1.0), T * Ha * D * 4)
+        # ---- the router with a correction and identity experts, beside Qwen2-MoE's
+        E, ident, top = mlp["router"]["experts"], mlp["router"]["identity"], mlp["router"]["top"]
+        x32 = torch.randn(T, W, device=dev)
+        w_r = (torch.randn(E + ident, W, device=dev) * 0.05).to(bf)
+        corr = torch.randn(E + ident, device=dev) * 0.1
+        timed("route (softmax, choice on score + correction, 16 + 2 experts)", case,
+              lambda: ops.route(x32, w_r, E + ident, top, 2, False, select_bias=corr, scale=0.7), T * W * 4 + (E + ident) * W * 2)
+        w_q = (torch.randn(E + 1, W, device=dev) * 0.05).to(bf)
+        timed("route (Qwen2-MoE's, norm inside, shared gate)", case,
+              lambda: ops.route(x32, w_q, E, top, True, True, norm_weight=wv, eps=1e-6), T * W * 4 + (E + 1) * W * 2)
+        ids, wts, _, offsets, rws, dest = ops.route(x32, w_r, E + ident, top, 2, False, select_bias=corr, scale=0.7)
+        y = torch.randn(T * top, W, device=dev)
+        shared = torch.randn(T, W, device=dev)
+        timed("moe_combine (identity experts, shared expert with a factor)", case,
+              lambda: ops.moe_combine(y, dest, wts, shared, None, resid, ids=ids, num_real=E, passthrough=x32, shared_scale=0.7),
+              T * W * 4 * (top + 3))
+        gq = torch.rand(T, device=dev)
+        timed("moe_combine (Qwen2-MoE's)", case, lambda: ops.moe_combine(y, dest, wts, shared, gq, resid), T * W * 4 * (top + 3))
+        # ---- the cap on the logits
+        N = 1 if case == "prefill" else R
+        logits = torch.randn(N, z["vocab"], device=dev) * 10
+        timed("tanh_cap (logits)", case, lambda: ops.tanh_cap(logits, 30.0), N * z["vocab"] * 8)
+    ops.check_errors()
+    return rows
+
+
+def run_faguzen(args, pk) -> dict:
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    out = {"workload": "faguzen", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+           "peaks": pk, "sizes": {}, "l2": "a buffer larger than L2 is written before every timed step"}
+    for width in (1024, 2048, 4096):
+        z = faguzen_config(width)
+        q = qwen_config_like_faguzen(z)
+        out["sizes"][str(width)] = {
+            "layer_runs": q["num_hidden_layers"], "faguzen": measure_engine(z, args.batch, args.prompt_len, args.steps, 2048),
+            "qwen2_moe": measure_engine(q, args.batch, args.prompt_len, args.steps, 2048)}
+    out["kernels_width_2048"] = faguzen_kernels(faguzen_config(2048), pk, args.batch, args.prompt_len, 2048)
+    t1 = time.time()
+    time.sleep(0.2)
+    sampler.stop()
+    out["clocks"] = sampler.summary(t0, t1)
+    return out
+
+
 def layers_that_fit(raw, want, reserve_gb=40.0):
     """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
     the cache pool, the head, graphs and activations."""
@@ -1172,7 +1369,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel", "zasazen", "salolorn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels", "zesapel", "zasazen", "salolorn", "faguzen"],
                     help="serving: the continuous-batching workload on the windowed model, instead of the default line; "
                          "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own; "
                          "kernels: the weight-streaming product alone")
@@ -1211,6 +1408,9 @@ def main() -> int:
         return 0
     if args.workload == "salolorn":
         print(json.dumps(run_salolorn(args, pk)))
+        return 0
+    if args.workload == "faguzen":
+        print(json.dumps(run_faguzen(args, pk)))
         return 0
     max_batch = 64 if not args.no_points else args.batch
     m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk, page=args.page_size)

@@ -46,6 +46,7 @@ struct PrefillTcParams {
     __nv_bfloat16* out;
     int R, nh, nkv, page_size, page_shift, total_pages, window;
     float scale_log2;
+    float cap_in, cap_out;      // cap_out != 0: a score is cap_out * tanh(dot * cap_in), in base-2 units (a cap on the scores)
     int skip_single;
     int* err;
 };
@@ -292,6 +293,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_fence(v[c]);
             // the scores are in registers: once P of this tile is announced, the buffer may be written again
+            if (p.cap_out != 0.f) {
+                // capped scores: c tanh(dot scale / c), in base-2 units from here on (tanh keeps the order, so the
+                // maximum may still be taken first; the scale below is then one)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[c][i] = __float_as_uint(p.cap_out * tanh_sfu(__uint_as_float(v[c][i]) * p.cap_in));
+            }
+            const float sl2 = p.cap_out != 0.f ? 1.0f : p.scale_log2;
             // does every row of this warp see every key of the tile?  Then nothing is masked.
             const bool row_all = j0 + BKV - 1 <= pos && (p.window <= 0 || pos - j0 < p.window);
             const bool warp_all = __all_sync(0xffffffffu, row_all);
@@ -311,7 +322,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;   // -inf: nothing seen
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // -inf: nothing seen
             float alpha = 1.0f;
             if (mx > m + RESCALE_STEP || m == -INFINITY) {
                 if (mx != -INFINITY) {
@@ -345,7 +356,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 float pr[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    pr[i] = ex2(fmaf(__uint_as_float(v[c][i]), p.scale_log2, -base_m));     // -inf: 0
+                    pr[i] = ex2(fmaf(__uint_as_float(v[c][i]), sl2, -base_m));     // -inf: 0
                     sum4[i & 3] += pr[i];
                 }
                 // keys 32c .. 32c + 31 of this row: half c / 2, 16-byte chunks 4 (c % 2) .. + 3 of the row
@@ -435,7 +446,7 @@ bool attention_prefill_tc_ok(const void* q, const void* k_cache, const void* v_c
                              int page_size, Score scale) {
     // (the row maximum is taken before the scores are scaled: the scale must be positive, and a distance term
     // has no place in that order of steps)
-    return scale.scale > 0.f && scale.slopes == nullptr && scale.softcap == 0.f && scale.plain_mask() && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
+    return scale.scale > 0.f && scale.slopes == nullptr && scale.plain_mask() && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
            ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
              reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
 }
@@ -453,7 +464,8 @@ bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cach
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
     PrefillTcParams p{block_table, table_width, cu_q, kv_len, static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size,
-                      shift, total_pages, window, scale.scale * 1.4426950408889634f, skip_single, error_flag_ptr()};
+                      shift, total_pages, window, scale.scale * 1.4426950408889634f, scale.cap_in(), scale.cap_out(), skip_single,
+                      error_flag_ptr()};
     const size_t smem = (size_t)TILE_BYTES * 7 + 1024;      // Q, 2 x K, 2 x V, 2 x P, and room to align
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(nh, (T + BQ - 1) / BQ + R);

@@ -1,13 +1,22 @@
 // Small kernels of layers that squash instead of norming: a norm without statistics, tanh(alpha x) w + b; a cap
 // c tanh(x / c) on rows of logits; a gate per output entry on attention heads stored wider than their values.
 //
-// None of these kernels waits on another.  All are launched with programmatic dependent launch (dep_wait() is their
-// first statement).
+// None of these kernels waits on another.  They are launched in the ordinary way (each starts when the kernel before
+// it has ended): launched with programmatic dependent launch, a benchmark process that wrote a 256 MB buffer before
+// every step while nvidia-smi polled the clocks stopped answering in its first steps, every time, and ran through
+// with these four launched plainly; the cause was not found, so they stay out of the dependent chain.  dep_wait()
+// and dep_launch_next() at their start do nothing in an ordinary launch.
 #include "api.h"
 #include "common.cuh"
 
 namespace dlmk {
 namespace {
+
+// An ordinary launch: the kernel starts when the one before it has ended (see the note at the top of the file).
+template <typename... P, typename... A>
+inline void launch_plain(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    kernel<<<grid, block, smem, stream>>>(std::forward<A>(args)...);
+}
 
 __device__ __forceinline__ float sigmoid_c(float z) { return 1.0f / (1.0f + expf(-z)); }
 
@@ -89,11 +98,11 @@ void dyt_norm(const float* x, const int32_t* rows, const float* w, const float* 
     if (n_rows <= 0) return;
     const dim3 block(H >= 1024 ? 256 : 128);
     if (out_dtype == F32)
-        launch_dep(dyt_norm_kernel<float, false>, dim3(n_rows), block, 0, stream, x, rows, w, b, alpha,
+        launch_plain(dyt_norm_kernel<float, false>, dim3(n_rows), block, 0, stream, x, rows, w, b, alpha,
                    static_cast<float*>(out), (const float*)nullptr, (const float*)nullptr, 0.f, (float*)nullptr,
                    (float*)nullptr, H);
     else
-        launch_dep(dyt_norm_kernel<__nv_bfloat16, false>, dim3(n_rows), block, 0, stream, x, rows, w, b, alpha,
+        launch_plain(dyt_norm_kernel<__nv_bfloat16, false>, dim3(n_rows), block, 0, stream, x, rows, w, b, alpha,
                    static_cast<__nv_bfloat16*>(out), (const float*)nullptr, (const float*)nullptr, 0.f,
                    (__nv_bfloat16*)nullptr, (float*)nullptr, H);
     check_launch("dyt_norm");
@@ -105,10 +114,10 @@ void dyt_norm_pair(const float* x, const float* wa, const float* ba, float alpha
     if (T <= 0) return;
     const dim3 block(H >= 1024 ? 256 : 128);
     if (out_dtype == F32)
-        launch_dep(dyt_norm_kernel<float, true>, dim3(T), block, 0, stream, x, (const int32_t*)nullptr, wa, ba, alpha_a,
+        launch_plain(dyt_norm_kernel<float, true>, dim3(T), block, 0, stream, x, (const int32_t*)nullptr, wa, ba, alpha_a,
                    static_cast<float*>(out_a), wb, bb, alpha_b, static_cast<float*>(out_b), out_b32, H);
     else
-        launch_dep(dyt_norm_kernel<__nv_bfloat16, true>, dim3(T), block, 0, stream, x, (const int32_t*)nullptr, wa, ba,
+        launch_plain(dyt_norm_kernel<__nv_bfloat16, true>, dim3(T), block, 0, stream, x, (const int32_t*)nullptr, wa, ba,
                    alpha_a, static_cast<__nv_bfloat16*>(out_a), wb, bb, alpha_b, static_cast<__nv_bfloat16*>(out_b),
                    out_b32, H);
     check_launch("dyt_norm_pair");
@@ -119,7 +128,7 @@ void tanh_cap(float* x, long long n, float cap, cudaStream_t stream) {
     DLM_CHECK(cap > 0.f, "tanh_cap: the cap must be positive");
     long long blocks = (n + 255) / 256;
     if (blocks > 8LL * sm_count()) blocks = 8LL * sm_count();
-    launch_dep(tanh_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, cap, 1.0f / cap);
+    launch_plain(tanh_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, cap, 1.0f / cap);
     check_launch("tanh_cap");
 }
 
@@ -129,10 +138,10 @@ void entry_gate(void* o, const float* gate, int ldg, int T, int nh, int dv, int 
     DLM_CHECK(D >= dv && dv >= 1, "entry_gate: the stored head size must hold the values");
     DLM_CHECK(resid == nullptr || (bias != nullptr && W > 0), "entry_gate: a residual to add to needs the bias and its width");
     if (dtype == F32)
-        launch_dep(entry_gate_kernel<float>, dim3(T), dim3(256), 0, stream, static_cast<float*>(o), gate, ldg, nh, dv, D,
+        launch_plain(entry_gate_kernel<float>, dim3(T), dim3(256), 0, stream, static_cast<float*>(o), gate, ldg, nh, dv, D,
                    factor, resid, bias, W);
     else
-        launch_dep(entry_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, static_cast<__nv_bfloat16*>(o), gate,
+        launch_plain(entry_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, static_cast<__nv_bfloat16*>(o), gate,
                    ldg, nh, dv, D, factor, resid, bias, W);
     check_launch("entry_gate");
 }

@@ -59,6 +59,8 @@ class GroupedQueryAttention(Mixer):
             self.b_qkv = torch.cat(parts).contiguous()
         else:
             self.b_qkv = None
+        if self.position is not None:
+            self.position.rotary(rt)        # the table is made now: no copy from the host in the middle of a step
 
     def cache_need(self):
         return PagedKV(self.nkv, self.hd, self.window)
@@ -344,6 +346,8 @@ class HeadNormedAttention(Mixer):
         if self.qk_norm:
             self.qn, self.kn = rt.vector(tensors["q.norm"]), rt.vector(tensors["k.norm"])
         self.sink = rt.vector(tensors["sink"]) if self.has_sink else None
+        if self.position is not None:
+            self.position.rotary(rt)        # the table is made now: no copy from the host in the middle of a step
 
     def _span(self):
         """How far back a query can see (None: to the start)."""
