@@ -2,17 +2,16 @@
 // c tanh(x / c) on rows of logits; a gate per output entry on attention heads stored wider than their values.
 //
 // None of these kernels waits on another.  They are launched in the ordinary way (each starts when the kernel before
-// it has ended): launched with programmatic dependent launch, a benchmark process that wrote a 256 MB buffer before
-// every step while nvidia-smi polled the clocks stopped answering in its first steps, every time, and ran through
-// with these four launched plainly; the cause was not found, so they stay out of the dependent chain.  dep_wait()
-// and dep_launch_next() at their start do nothing in an ordinary launch.
+// it has ended); dep_wait() and dep_launch_next() at their start then do nothing.  The one design that uses them so
+// far runs all its steps without programmatic dependent launch (see its model file), and these kernels have not been
+// run in a dependent chain since.
 #include "api.h"
 #include "common.cuh"
 
 namespace dlmk {
 namespace {
 
-// An ordinary launch: the kernel starts when the one before it has ended (see the note at the top of the file).
+// An ordinary launch: the kernel starts when the one before it has ended.
 template <typename... P, typename... A>
 inline void launch_plain(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
     kernel<<<grid, block, smem, stream>>>(std::forward<A>(args)...);

@@ -73,7 +73,10 @@ def build_spec(cfg: FaguzenConfig) -> ModelSpec:
     return ModelSpec(hidden_size=cfg.width, vocab_size=cfg.vocab, layers=layers, layer_prefixes=prefixes,
                      final_norm=norm, final_norm_prefix="final.norm", embed_name="embed", lm_head_name="head",
                      order=layer_order(len(cfg.layers), cfg.loop), pass_entry=entry, pass_entry_prefix="loop.",
-                     logit_softcap=cfg.logit_softcap)
+                     logit_softcap=cfg.logit_softcap,
+                     # This design's steps stopped answering now and then when the clocks were polled beside them and
+                     # its kernels were launched dependently; with ordinary launches they did not, so it takes those.
+                     dependent_launch=False)
 
 
 register_architecture(FaguzenConfig.architecture, FaguzenConfig, build_spec, model_type=FaguzenConfig.model_type)

@@ -92,6 +92,21 @@ class NativeOps:
             self._side = torch.cuda.Stream()
         return _Branch(self._side)
 
+    def dependent_launch(self, on: bool):
+        """A context in which the short kernels are (on) or are not (off) launched with programmatic dependent
+        launch; the library's setting is put back at the end."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def scope():
+            before = bool(self.k.dep_launch_enabled())
+            self.k.set_dep_launch(bool(on) and before)      # never switched on where the process has it off
+            try:
+                yield
+            finally:
+                self.k.set_dep_launch(before)
+        return scope()
+
     def check_errors(self) -> None:
         """Raises if a kernel refused an access (page or token id outside its table)."""
         flag = self.k.take_error_flag()

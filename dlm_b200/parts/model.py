@@ -42,6 +42,8 @@ class ModelSpec:
     pass_entry: PartSpec | None = None       # what makes the input of a repeated run's pass (calls with ``enters_pass``)
     pass_entry_prefix: str = ""              # tensor-name prefix of that part's tensors
     logit_softcap: float = 0.0               # c > 0: the logits are ``c tanh(head product / c)``
+    dependent_launch: bool = True            # False: this model's steps launch every kernel in the ordinary way (each
+                                             # starts when the one before it has ended) where the backend has the choice
 
 
 class WeightError(ValueError):
@@ -163,6 +165,13 @@ class DecoderModel:
     def step(self, batch: StepBatch, cache) -> torch.Tensor:
         """Runs the batch's tokens through every call of the order, reading and writing
         ``cache``; returns 32-bit logits ``[len(batch.logit_rows), vocab]``."""
+        rt, ops = self.rt, self.rt.ops
+        if not self.spec.dependent_launch and hasattr(ops, "dependent_launch"):
+            with ops.dependent_launch(False):
+                return self._step(batch, cache)
+        return self._step(batch, cache)
+
+    def _step(self, batch: StepBatch, cache) -> torch.Tensor:
         rt, ops = self.rt, self.rt.ops
 
         def paged(call):
