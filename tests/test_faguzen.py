@@ -58,6 +58,7 @@ def test_registry_resolves_the_architecture_and_round_trips_the_config():
         assert len(spec.layers) == len(cfg["layers"]) and spec.vocab_size == cfg["vocab"]
         assert not spec.tie_word_embeddings and (spec.pass_entry is not None) == ("loop" in cfg)
         assert spec.logit_softcap == cfg.get("logit_softcap", 0.0)
+        assert spec.dependent_launch is False          # this design's steps take ordinary launches
         assert len(spec.order) == runs_of(cfg)
         assert FaguzenConfig.from_dict(typed.to_dict()) == typed
         assert typed.to_dict()["layers"] == cfg["layers"]

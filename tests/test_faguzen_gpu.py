@@ -365,6 +365,29 @@ def test_a_single_layer(mlp, loop, rot, tmp_path):
         assert worst_error(cuttings.run_trace(eng, steps), ref) < TOL["float32"]
 
 
+def test_steps_take_ordinary_launches_and_leave_the_setting_as_it_was(folders):
+    """The design's spec asks for ordinary launches: inside a step the library's switch is off, after it the switch
+    is what it was, whichever that was; another model's steps do not touch it."""
+    folder, _ = folders["B"]
+    eng = gpu_engine(folder, "float32")
+    k = eng.rt.ops.k
+    before = bool(k.dep_launch_enabled())
+    seen = []
+    eng.model.after_layer = lambda call, x: seen.append(bool(k.dep_launch_enabled()))
+    try:
+        for setting in (True, False):
+            k.set_dep_launch(setting)
+            seen.clear()
+            slot = eng.cache.open()
+            eng.step([(slot, tokens(1, 9, CONFIGS["B"]["vocab"]), [8])])
+            eng.cache.close(slot)
+            assert seen and not any(seen)
+            assert bool(k.dep_launch_enabled()) is setting
+    finally:
+        k.set_dep_launch(before)
+        eng.model.after_layer = None
+
+
 def test_residual_after_every_layer_run(folders):
     folder, oracle = folders["A"]
     toks = tokens(3, 50, CONFIGS["A"]["vocab"])
