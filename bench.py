@@ -1121,14 +1121,14 @@ def faguzen_config(width, vocab=32768):
     `width`; the last layer has no feed-forward."""
     heads = width // 128
     mixer = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                      "softcap": 30.0, "rot": {"base": 1e4, "dims": 64,
-                                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}},
-             "right": {"heads": width // 128, "dim": 64, "vdim": 128, "gate_cap": 12.0}, "left_scale": 1.0, "right_scale": 1.0}
+                      "softcap": 50.0, "rot": {"base": 1e6, "dims": 64,
+                                               "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 8192}}},
+             "right": {"heads": width // 128, "dim": 64, "vdim": 128, "gate_cap": 15.0}, "left_scale": 1.0, "right_scale": 1.0}
     mlp = {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 2}, "expert": {"ff": width // 2},
            "shared": {"ff": width}}
     layers = [{"type": "parallel", "mixer": mixer, "mlp": mlp} for _ in range(3)] + [{"type": "parallel", "mixer": mixer, "mlp": None}]
-    return {"architecture": "Faguzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
-            "logit_softcap": 30.0, "max_positions": 8192, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
+    return {"architecture": "Faguzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.8,
+            "logit_softcap": 25.0, "max_positions": 8192, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
 
 
 def qwen_config_like_faguzen(z):
@@ -1243,7 +1243,7 @@ def faguzen_kernels(z, pk, batch, context, prefill_tokens):
         v_cache = (torch.randn(R * pages_each + 1, Ga, 64, D, device=dev) * 0.3).to(bf)
         aq = torch.randn(T, (Ha + Ga) * da + Ga * dva + Ha * dva, device=dev)
         rd = lf["rot"]["dims"]
-        freq = torch.tensor([1e4 ** (-2.0 * i / rd) for i in range(rd // 2)], device=dev)
+        freq = torch.tensor([lf["rot"]["base"] ** (-2.0 * i / rd) for i in range(rd // 2)], device=dev)
         io = T * ((Ha + Ga) * da + Ga * dva) * 4 + T * (Ha + 2 * Ga) * D * 2
         timed("head_norm_rope_write (no norms, half of each head rotated)", case,
               lambda: ops.head_norm_rope_write(aq, b.positions, None, None, 1e-6, freq, rd, False, slots, k_cache, v_cache,
@@ -1270,22 +1270,22 @@ def faguzen_kernels(z, pk, batch, context, prefill_tokens):
         w_r = (torch.randn(E + ident, W, device=dev) * 0.05).to(bf)
         corr = torch.randn(E + ident, device=dev) * 0.1
         timed("route (softmax, choice on score + correction, 16 + 2 experts)", case,
-              lambda: ops.route(x32, w_r, E + ident, top, 2, False, select_bias=corr, scale=0.7), T * W * 4 + (E + ident) * W * 2)
+              lambda: ops.route(x32, w_r, E + ident, top, 2, False, select_bias=corr, scale=0.8), T * W * 4 + (E + ident) * W * 2)
         w_q = (torch.randn(E + 1, W, device=dev) * 0.05).to(bf)
         timed("route (Qwen2-MoE's, norm inside, shared gate)", case,
               lambda: ops.route(x32, w_q, E, top, True, True, norm_weight=wv, eps=1e-6), T * W * 4 + (E + 1) * W * 2)
-        ids, wts, _, offsets, rws, dest = ops.route(x32, w_r, E + ident, top, 2, False, select_bias=corr, scale=0.7)
+        ids, wts, _, offsets, rws, dest = ops.route(x32, w_r, E + ident, top, 2, False, select_bias=corr, scale=0.8)
         y = torch.randn(T * top, W, device=dev)
         shared = torch.randn(T, W, device=dev)
         timed("moe_combine (identity experts, shared expert with a factor)", case,
-              lambda: ops.moe_combine(y, dest, wts, shared, None, resid, ids=ids, num_real=E, passthrough=x32, shared_scale=0.7),
+              lambda: ops.moe_combine(y, dest, wts, shared, None, resid, ids=ids, num_real=E, passthrough=x32, shared_scale=0.8),
               T * W * 4 * (top + 3))
         gq = torch.rand(T, device=dev)
         timed("moe_combine (Qwen2-MoE's)", case, lambda: ops.moe_combine(y, dest, wts, shared, gq, resid), T * W * 4 * (top + 3))
         # ---- the cap on the logits
         N = 1 if case == "prefill" else R
         logits = torch.randn(N, z["vocab"], device=dev) * 10
-        timed("tanh_cap (logits)", case, lambda: ops.tanh_cap(logits, 30.0), N * z["vocab"] * 8)
+        timed("tanh_cap (logits)", case, lambda: ops.tanh_cap(logits, z["logit_softcap"]), N * z["vocab"] * 8)
     ops.check_errors()
     return rows
 

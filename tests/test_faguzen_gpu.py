@@ -94,9 +94,9 @@ def test_cap_on_logits_and_gate_per_entry(ops, dtype):
     ref = PlainOps()
     x = randn(7, 333, seed=1, std=20.0)
     want = x.clone().cpu()
-    ref.tanh_cap(want, 15.0)
-    ops.tanh_cap(x, 15.0)
-    assert torch.allclose(x.cpu(), want, atol=1e-5, rtol=1e-5) and float(x.abs().max()) <= 15.0
+    ref.tanh_cap(want, 12.5)
+    ops.tanh_cap(x, 12.5)
+    assert torch.allclose(x.cpu(), want, atol=1e-5, rtol=1e-5) and float(x.abs().max()) <= 12.5
     for T, nh, dv, D in ((5, 6, 40, 48), (33, 2, 64, 64), (2, 3, 5, 16), (300, 8, 96, 128)):
         o = randn(T, nh * D, seed=2, dtype=dtype)
         wide = randn(T, nh * dv + 9, seed=3, std=2.0)
@@ -117,7 +117,7 @@ def test_cap_on_logits_and_gate_per_entry(ops, dtype):
 
 
 @pytest.mark.parametrize("heads,dk,dv", [(3, 10, 14), (1, 46, 38), (2, 64, 128), (4, 32, 64), (2, 128, 64), (6, 8, 4),
-                                         (2, 48, 48), (1, 200, 24)])
+                                         (2, 40, 56), (1, 200, 24)])
 def test_memory_scan_against_its_plain_statement(ops, heads, dk, dv):
     """The matrix memory with a running maximum; inputs are column slices of a wider matrix; three requests whose
     states lie in slots of their own and are not zero at the start."""
@@ -246,7 +246,7 @@ CAP_CASES = [
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,ps,reqs", CAP_CASES)
 @pytest.mark.parametrize("fast", [False, True])
-@pytest.mark.parametrize("cap", [2.0, 30.0])
+@pytest.mark.parametrize("cap", [2.0, 25.0])
 def test_attention_with_capped_scores(ops, slow_ops, dtype, nh, nkv, hd, ps, reqs, fast, cap):
     """Every attention kernel (FMA, warp-level prefill, both decode kernels) with squashed scores: a small cap that
     bends most scores and a large one that bends few."""
