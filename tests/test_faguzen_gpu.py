@@ -562,3 +562,30 @@ def test_a_wider_model_with_a_long_request(dtype, tmp_path):
             assert max(r) < 1.0, (what, max(r))
         else:
             assert mostly_within_limits(got, ref, lim, ok), (what, max(r))
+
+
+ODD = {"architecture": "Faguzen", "vocab": 1001, "width": 200, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+       "logit_softcap": 7.0, "loop": {"start": 1, "stop": 3, "times": 2},
+       "layers": [layer(left(2, 2, 160, 72, 0.08, 11.0, 1e4, 160, {"factor": 2.0, "low": 2.0, "high": 16.0, "original": 512}),
+                        right(1, 200, 300, 3.0), 0.3, 2.0, moe(33, 7, 6, 24, 88)),
+                  layer(left(12, 4, 16, 8, 0.25, 1.5, 20.0, 2), right(5, 4, 3, 30.0), 1.5, 0.2, moe(1, 1, 1, 40)),
+                  layer(left(3, 3, 80, 48, 0.1, 40.0), right(2, 72, 40, 8.0), 1.0, 1.0)]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unusual_sizes(dtype, tmp_path):
+    """Heads wider than any tensor-core kernel takes (160) and tiny ones (16 x 8, 4 x 3), a memory of 200 x 300, a single
+    memory head, more experts than a warp has lanes with six a token, one expert beside one identity expert, a loop
+    that ends with the last layer, a rotation over two entries, a vocabulary that is no multiple of anything."""
+    tensors = write_model(ODD, str(tmp_path / "m"), seed=11)
+    oracle = plain.PlainFaguzen(ODD, tensors)
+    reqs = {f"r{i}": tokens(i, n, ODD["vocab"]) for i, n in enumerate([3, 70, 260])}
+    ref, lim, ok = references(oracle, reqs, dtype, carry=12 if dtype == "bfloat16" else None)
+    eng = gpu_engine(str(tmp_path / "m"), dtype, page_size=64, num_pages=24)
+    mixed, _ = cuttings.mixed(reqs, max_live=3, seed=2, decode_tail=30)
+    for what, steps in (("whole", cuttings.whole(reqs)), ("decode", cuttings.tail_decode(reqs, 60)),
+                        ("portions", cuttings.portions(reqs)), ("mixed", mixed)):
+        got = cuttings.run_trace(eng, steps)
+        eng.rt.ops.check_errors()
+        r = ratios(got, ref, lim, ok)
+        assert (max(r) < 1.0) if dtype == "float32" else mostly_within_limits(got, ref, lim, ok), (what, max(r))
